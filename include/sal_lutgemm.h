@@ -1,0 +1,163 @@
+/*
+ * sal_lutgemm.h — C ABI of the B200 (sm_100a) BCQ LUT-GEMV library.
+ *
+ * The library replaces the compiled `lutgemm` extension of ShiftAddLLM
+ * (lut_gemm/lutgemm_cuda.cpp + lutgemm_cuda_kernel.cu + mv_fp16_bias.hpp).
+ * Each compute entry point below names the reference function it stands in
+ * for.  All pointers are DEVICE pointers owned by the caller unless stated
+ * otherwise; the library keeps no state between calls and allocates nothing
+ * on the compute path.  `stream` is a cudaStream_t passed as void* (NULL =
+ * legacy default stream).  Every function returns SAL_OK (0) or a negative
+ * SAL_E_* code; nothing is thrown and nothing is printed.
+ *
+ * Dimension names: K = in_features, N = out_features, M = rows (tokens),
+ * q = bit planes (`nb`), num_groups as in the reference's argument lists.
+ *
+ * Common layouts (identical to the reference, mv_fp16_bias.hpp:52,86-90):
+ *   bw     uint32 [K/32][q][N]   bit t of word kk = input feature 32*kk+t, set = +1
+ *   x      fp16   [M][K]
+ *   y      fp16   [M][N]
+ *   bias   fp16   [N] or NULL
+ *
+ * Result: y = (flags & SAL_ACCUMULATE ? y : 0) + bias + sum_b alpha_b * (B_b^T x).
+ * The reference kernels add into `output` (mv_fp16_bias.hpp:101); its callers
+ * pre-load the bias there (lut_gemm/quant.py:46).  SAL_ACCUMULATE reproduces
+ * that contract; without it the bias add is fused and y is overwritten.
+ * Accumulation is fp32 and the split-K reduction order is fixed, so results
+ * are deterministic (the reference accumulates in fp16 with atomics).
+ */
+#ifndef SAL_LUTGEMM_H
+#define SAL_LUTGEMM_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAL_VERSION 100
+
+/* status codes */
+#define SAL_OK 0
+#define SAL_E_NULL (-1)        /* a required pointer is NULL */
+#define SAL_E_SHAPE (-2)       /* K % 32, group divisibility, q or M out of range ... */
+#define SAL_E_ALIGN (-3)       /* pointer not 16-byte aligned */
+#define SAL_E_WORKSPACE (-4)   /* workspace missing or too small */
+#define SAL_E_LAUNCH (-5)      /* CUDA launch or runtime error */
+#define SAL_E_UNSUPPORTED (-6) /* valid but not implemented for this shape */
+#define SAL_E_DEVICE (-7)      /* no sm_100 device / wrong architecture */
+#define SAL_E_TIMEOUT (-8)     /* a bounded device-side wait gave up (read back from the workspace) */
+
+/* flags */
+#define SAL_ACCUMULATE 1u  /* y += result (reference semantics) instead of y = bias + result */
+#define SAL_PDL 2u         /* launch with programmatic dependent launch: the packed planes are
+                              prefetched while the previous kernel of the stream drains */
+#define SAL_FORCE_GENERIC 4u /* use the shape-agnostic kernel even where the tiled one applies */
+
+#define SAL_MAX_Q 8
+#define SAL_MAX_M 64
+#define SAL_MAX_GROUP 8 /* problems per grouped launch */
+
+int sal_version(void);
+const char *sal_status_string(int status);
+
+/* Device check: SAL_OK when the current device is compute capability 10.x. */
+int sal_device_ok(void);
+
+/*
+ * Scratch ("workspace") for the deterministic split-K reduction.  The caller
+ * allocates `sal_workspace_bytes(M, N)` bytes of device memory once, zero-fills
+ * it once (cudaMemset), and may reuse it for any later call whose M and N are
+ * not larger.  Calls sharing one workspace must be ordered on one stream.
+ * For a grouped launch pass the sum of N over the group.
+ */
+size_t sal_workspace_bytes(int M, int N);
+
+/* Reads back (synchronously, on `stream`) and clears the device-side status
+ * word of a workspace: SAL_OK or SAL_E_TIMEOUT. */
+int sal_workspace_status(void *workspace, void *stream);
+
+/*
+ * Mode A ("row-wise groups"): alpha fp16 [num_groups][q][N], group = K/num_groups
+ * consecutive input features.  Replaces lutgemm_compute_shift_scale
+ * (lutgemm_cuda.cpp:43-52 -> lutgemm_cuda_kernel.cu:268-285 -> mv_fp16_bias.hpp:498-579,
+ * 766-774).  The reference handles M = 1 only; here 1 <= M <= SAL_MAX_M.
+ */
+int sal_lutgemv_shift_scale(const void *bw, const void *alpha, const void *bias, const void *x, void *y,
+                            int M, int K, int N, int q, int num_groups, unsigned flags,
+                            void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * One alpha per (group, column), halved for each successive plane, plus an
+ * offset term q_bias[g][n] * sum_{k in g} x[k].  alpha, q_bias fp16 [num_groups][N].
+ * Replaces lutgemm_compute (lutgemm_cuda.cpp:88-98 -> lutgemm_cuda_kernel.cu:288-316
+ * -> mv_fp16_bias.hpp:8-103, 726-734).
+ */
+int sal_lutgemv_compute(const void *bw, const void *alpha, const void *q_bias, const void *bias,
+                        const void *x, void *y, int M, int K, int N, int q, int num_groups,
+                        unsigned flags, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Mode B ("block"): one multiplier per block of 8 input features x (N/num_groups)
+ * output features; alpha [K/8][q][num_groups].
+ *   sal_lutgemm_block            alpha fp16                      replaces lutgemm_compute_block
+ *       (lutgemm_cuda.cpp:54-63 -> lutgemm_cuda_kernel.cu:319-347 -> mv_fp16_bias.hpp:105-220)
+ *   sal_lutgemm_block_shift      alpha uint16, three 3-bit exponents, multiplier
+ *       2^(a&7)+2^((a>>3)&7)+2^((a>>6)&7)                        replaces lutgemm_compute_block_shift
+ *       (lutgemm_cuda.cpp:65-74 -> lutgemm_cuda_kernel.cu:350-378 -> mv_fp16_bias.hpp:223-328)
+ *   sal_lutgemm_block_shift_int8 alpha int8 [K/8][q][num_groups][3], multiplier sum of 2^s
+ *       over the three shifts, -128 meaning "no term"            replaces lutgemm_compute_block_shiftInt8
+ *       (lutgemm_cuda.cpp:76-85 -> lutgemm_cuda_kernel.cu:380-408 -> mv_fp16_bias.hpp:342-495);
+ *       this is the call LutLinear.forward makes (lut_gemm/quant.py:50-51).
+ * x fp16 [M][K], y fp16 [M][N], 1 <= M <= SAL_MAX_M.
+ */
+int sal_lutgemm_block(const void *bw, const void *alpha, const void *bias, const void *x, void *y,
+                      int M, int K, int N, int q, int num_groups, unsigned flags,
+                      void *workspace, size_t workspace_bytes, void *stream);
+int sal_lutgemm_block_shift(const void *bw, const void *alpha_u16, const void *bias, const void *x, void *y,
+                            int M, int K, int N, int q, int num_groups, unsigned flags,
+                            void *workspace, size_t workspace_bytes, void *stream);
+int sal_lutgemm_block_shift_int8(const void *bw, const void *alpha_i8, const void *bias, const void *x, void *y,
+                                 int M, int K, int N, int q, int num_groups, int num_apot, unsigned flags,
+                                 void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Grouped mode-A launch: up to SAL_MAX_GROUP independent products in ONE kernel
+ * (e.g. q/k/v of one decoder layer, or gate/up), so the weight stream does not
+ * stop at problem boundaries.  No counterpart in the reference, which issues
+ * one launch per linear layer (lut_gemm/quant.py:41-54).  `problems` is a HOST
+ * array; it is copied into the launch parameters.
+ */
+typedef struct sal_problem {
+    const void *bw;    /* uint32 [K/32][q][N] */
+    const void *alpha; /* fp16 [num_groups][q][N] */
+    const void *bias;  /* fp16 [N] or NULL */
+    const void *x;     /* fp16 [M][K] */
+    void *y;           /* fp16 [M][N] */
+    int M, K, N, q, num_groups;
+} sal_problem;
+
+int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags,
+                        void *workspace, size_t workspace_bytes, void *stream);
+
+/* Introspection for tests and the benchmark: which kernel a mode-A call would
+ * use (1 = tiled TMA kernel, 0 = generic) and its launch geometry. */
+typedef struct sal_plan_info {
+    int tiled;
+    int ctas;
+    int ranges;      /* column ranges */
+    int splits;      /* K splits */
+    int stages;
+    int smem_bytes;
+} sal_plan_info;
+int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_info *out);
+
+/* Measurement hook: caps the depth of the shared-memory ring of the tiled kernel
+ * (0 = as deep as shared memory allows).  Process-wide; not for production use. */
+int sal_debug_set_stages(int stages);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAL_LUTGEMM_H */

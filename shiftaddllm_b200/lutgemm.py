@@ -1,0 +1,168 @@
+"""Drop-in for the reference's compiled ``lutgemm`` extension.
+
+Same five function names, argument order and in-place accumulate semantics as
+lut_gemm/lutgemm_cuda.cpp:43-98, 225-230; the work is done by the sm_100a
+library behind the C ABI of ``include/sal_lutgemm.h``.  To make reference code
+that does ``import lutgemm`` pick this module up, call :func:`install`.
+
+Differences from the reference, all deliberate: arguments are validated
+(dtype, device, contiguity, shapes) and a bad call raises ``RuntimeError``
+instead of reading out of bounds; kernels run on torch's current stream, not
+the legacy default stream; accumulation is fp32 and deterministic; batch
+(``M > 1``) inputs are accepted by every entry point.
+"""
+from __future__ import annotations
+
+import sys
+
+import torch
+
+from . import _lib
+
+_workspaces: dict = {}
+
+
+def workspace_for(device: torch.device, m: int, n: int) -> torch.Tensor:
+    """Zero-initialised scratch for the split-K reduction, cached per
+    (device, stream) and grown on demand.  Calls on one stream are ordered, so
+    sharing one buffer per stream is race-free."""
+    lib = _lib.load()
+    stream = torch.cuda.current_stream(device).cuda_stream
+    key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
+    need = lib.sal_workspace_bytes(m, n)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(need, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def _req(t: torch.Tensor, dtype, name: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise RuntimeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if t.dtype != dtype:
+        raise RuntimeError(f"{name} must have dtype {dtype}, got {t.dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _rows(output: torch.Tensor, d_input: torch.Tensor, n: int, k: int):
+    if d_input.numel() % k or output.numel() % n:
+        raise RuntimeError("input/output sizes do not match kSize/mSize")
+    m = d_input.numel() // k
+    if output.numel() // n != m:
+        raise RuntimeError(f"output holds {output.numel() // n} rows but input holds {m}")
+    return m
+
+
+def _launch(fn_name, output, bWeight, alpha, alpha_dtype, d_input, mSize, kSize, nb, num_groups, *,
+            extra_ptr=None, num_apot=None, alpha_numel=None, flags=_lib.SAL_ACCUMULATE, bias=None):
+    lib = _lib.load()
+    _req(output, torch.float16, "output")
+    _req(bWeight, torch.int32, "bWeight")
+    _req(alpha, alpha_dtype, "alpha")
+    _req(d_input, torch.float16, "d_input")
+    n, k, q = int(mSize), int(kSize), int(nb)
+    if k % 32 or bWeight.numel() != (k // 32) * q * n:
+        raise RuntimeError(f"bWeight must hold (kSize/32)*nb*mSize = {(k // 32) * q * n} words, has {bWeight.numel()}")
+    if alpha_numel is not None and alpha.numel() != alpha_numel:
+        raise RuntimeError(f"alpha must hold {alpha_numel} elements, has {alpha.numel()}")
+    m = _rows(output, d_input, n, k)
+    dev = output.device
+    for t in (bWeight, alpha, d_input):
+        if t.device != dev:
+            raise RuntimeError("all tensors must live on the same device")
+    with torch.cuda.device(dev):
+        ws = workspace_for(dev, m, n)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        args = [bWeight.data_ptr(), alpha.data_ptr()]
+        if extra_ptr is not None:
+            args.append(extra_ptr)
+        args += [bias.data_ptr() if bias is not None else None, d_input.data_ptr(), output.data_ptr(), m, k, n, q,
+                 int(num_groups)]
+        if num_apot is not None:
+            args.append(int(num_apot))
+        args += [flags, ws.data_ptr(), ws.numel(), stream]
+        _lib.check(getattr(lib, fn_name)(*args), fn_name)
+
+
+def lutgemm_compute_shift_scale(output, bWeight, alpha, d_input, mSize, kSize, nb, num_groups):
+    """``output += sum_b alpha[g,b,:] * (B_b^T x)``; alpha fp16 ``[num_groups, nb, mSize]``
+    (lutgemm_cuda.cpp:43-52)."""
+    _launch("sal_lutgemv_shift_scale", output, bWeight, alpha, torch.float16, d_input, mSize, kSize, nb, num_groups,
+            alpha_numel=int(num_groups) * int(nb) * int(mSize))
+
+
+def lutgemm_compute(output, bWeight, alpha, q_bias, d_input, mSize, kSize, nb, num_groups):
+    """alpha, q_bias fp16 ``[num_groups, mSize]``; plane b scaled by ``alpha / 2**(b+1)``
+    (lutgemm_cuda.cpp:88-98)."""
+    _req(q_bias, torch.float16, "q_bias")
+    if q_bias.numel() != int(num_groups) * int(mSize):
+        raise RuntimeError("q_bias must hold num_groups*mSize elements")
+    _launch("sal_lutgemv_compute", output, bWeight, alpha, torch.float16, d_input, mSize, kSize, nb, num_groups,
+            extra_ptr=q_bias.data_ptr(), alpha_numel=int(num_groups) * int(mSize))
+
+
+def lutgemm_compute_block(output, bWeight, alpha, d_input, mSize, kSize, nb, num_groups):
+    """alpha fp16 ``[kSize/8, nb, num_groups]`` (lutgemm_cuda.cpp:54-63)."""
+    _launch("sal_lutgemm_block", output, bWeight, alpha, torch.float16, d_input, mSize, kSize, nb, num_groups,
+            alpha_numel=(int(kSize) // 8) * int(nb) * int(num_groups))
+
+
+def lutgemm_compute_block_shift(output, bWeight, alpha, d_input, mSize, kSize, nb, num_groups, num_apot):
+    """alpha int16 ``[kSize/8, nb, num_groups]``, three 3-bit exponents (lutgemm_cuda.cpp:65-74)."""
+    _launch("sal_lutgemm_block_shift", output, bWeight, alpha, torch.int16, d_input, mSize, kSize, nb, num_groups,
+            alpha_numel=(int(kSize) // 8) * int(nb) * int(num_groups))
+
+
+def lutgemm_compute_block_shiftInt8(output, bWeight, alpha, d_input, mSize, kSize, nb, num_groups, num_apot):
+    """alpha int8 ``[kSize/8, nb, num_groups, num_apot]`` (lutgemm_cuda.cpp:76-85); -128 = no term."""
+    _launch("sal_lutgemm_block_shift_int8", output, bWeight, alpha, torch.int8, d_input, mSize, kSize, nb, num_groups,
+            num_apot=num_apot, alpha_numel=(int(kSize) // 8) * int(nb) * int(num_groups) * int(num_apot))
+
+
+def lutgemv_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb, num_groups, *, pdl=False):
+    """Extension over the reference API: ``output = bias + product`` in one
+    kernel (no separate ``bias.clone()``), optionally launched with programmatic
+    dependent launch."""
+    flags = _lib.SAL_PDL if pdl else 0
+    _launch("sal_lutgemv_shift_scale", output, bWeight, alpha, torch.float16, d_input, mSize, kSize, nb, num_groups,
+            flags=flags, bias=bias, alpha_numel=int(num_groups) * int(nb) * int(mSize))
+
+
+def lutgemv_grouped(problems, *, pdl=False, accumulate=False):
+    """Several independent mode-A products in one launch.  ``problems`` is a list
+    of dicts with keys output, bWeight, alpha, bias (or None), d_input,
+    mSize, kSize, nb, num_groups."""
+    lib = _lib.load()
+    if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
+        raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
+    arr = (_lib.SalProblem * len(problems))()
+    dev = problems[0]["output"].device
+    n_total = 0
+    for i, p in enumerate(problems):
+        _req(p["output"], torch.float16, "output")
+        _req(p["bWeight"], torch.int32, "bWeight")
+        _req(p["alpha"], torch.float16, "alpha")
+        _req(p["d_input"], torch.float16, "d_input")
+        n, k = int(p["mSize"]), int(p["kSize"])
+        m = _rows(p["output"], p["d_input"], n, k)
+        bias = p.get("bias")
+        arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
+                                 bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
+                                 p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]))
+        n_total += n
+    flags = (_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
+    with torch.cuda.device(dev):
+        ws = workspace_for(dev, 1, n_total)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        _lib.check(lib.sal_lutgemv_grouped(arr, len(problems), flags, ws.data_ptr(), ws.numel(), stream),
+                   "sal_lutgemv_grouped")
+
+
+def install(name: str = "lutgemm") -> None:
+    """Registers this module as ``lutgemm`` so that unmodified reference code
+    (``import lutgemm`` in lut_gemm/quant.py:5) binds to the sm_100a library."""
+    sys.modules[name] = sys.modules[__name__]
