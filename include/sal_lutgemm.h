@@ -62,6 +62,10 @@ extern "C" {
 int sal_version(void);
 const char *sal_status_string(int status);
 
+/* Text of the last CUDA runtime error seen by this thread inside the library
+ * (what lies behind a SAL_E_LAUNCH). */
+const char *sal_last_cuda_error(void);
+
 /* Device check: SAL_OK when the current device is compute capability 10.x. */
 int sal_device_ok(void);
 
@@ -153,9 +157,11 @@ typedef struct sal_plan_info {
 } sal_plan_info;
 int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_info *out);
 
-/* Measurement hook: caps the depth of the shared-memory ring of the tiled kernel
- * (0 = as deep as shared memory allows).  Process-wide; not for production use. */
-int sal_debug_set_stages(int stages);
+/* Measurement hook, process-wide, not for production use.  Keys: "stages" caps the
+ * depth of the shared-memory ring of the tiled kernel (0 = as deep as fits);
+ * "budget_pct" scales the number of SMs the planner sizes its grid for
+ * (100 = one CTA per SM's worth of work, 200 = two). */
+int sal_debug_set(const char *key, int value);
 
 #ifdef __cplusplus
 }

@@ -36,6 +36,7 @@ class SalPlanInfo(ctypes.Structure):
 SIGNATURES = {
     "sal_version": (_i, []),
     "sal_status_string": (ctypes.c_char_p, [_i]),
+    "sal_last_cuda_error": (ctypes.c_char_p, []),
     "sal_device_ok": (_i, []),
     "sal_workspace_bytes": (_sz, [_i, _i]),
     "sal_workspace_status": (_i, [_vp, _vp]),
@@ -46,7 +47,7 @@ SIGNATURES = {
     "sal_lutgemm_block_shift_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemv_grouped": (_i, [ctypes.POINTER(SalProblem), _i, _u, _vp, _sz, _vp]),
     "sal_plan_shift_scale": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(SalPlanInfo)]),
-    "sal_debug_set_stages": (_i, [_i]),
+    "sal_debug_set": (_i, [ctypes.c_char_p, _i]),
 }
 
 _lib = None
@@ -75,4 +76,5 @@ def status_string(code: int) -> str:
 
 def check(code: int, what: str) -> None:
     if code != SAL_OK:
-        raise RuntimeError(f"{what} failed: {status_string(code)} (status {code})")
+        detail = f"; CUDA: {load().sal_last_cuda_error().decode()}" if code == SAL_E_LAUNCH else ""
+        raise RuntimeError(f"{what} failed: {status_string(code)} (status {code}){detail}")

@@ -9,11 +9,13 @@
 //
 // Tiled kernel (M = 1, mode A), per CTA:
 //   * one producer warp issues TMA bulk copies (cp.async.bulk + mbarrier
-//     complete_tx) of [8 words][q planes][CW columns] weight tiles plus the
-//     matching alpha rows into a multi-stage shared-memory ring.  The copies do
-//     not depend on the activations, so under programmatic dependent launch
-//     they are issued before griddepcontrol.wait and overlap the previous
-//     kernel's tail;
+//     complete_tx) of [8 words][q planes][CW columns] weight tiles into a
+//     shared-memory ring.  The copies do not depend on the activations, so
+//     under programmatic dependent launch they are issued before
+//     griddepcontrol.wait and overlap the previous kernel's tail.  A CTA uses
+//     at most half of an SM's shared memory, so the CTAs of two consecutive
+//     kernels are co-resident: one computes while the next one's weights land;
+//   * the alpha scales are read with plain loads, one tile ahead, into registers;
 //   * NCW consumer warps build the tables of one 256-feature K block in shared
 //     memory, "bank striped": entry e of chunk c sits at byte e*256 + 4*c (+128
 //     for odd K blocks, which double-buffers the table), so chunk c only ever
@@ -32,6 +34,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 #include "sal_lutgemm.h"
 
@@ -128,6 +132,33 @@ __device__ __forceinline__ void tma_bulk_g2s(uint32_t dst, const void *src, uint
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
+// prmt.b32, generic mode: selector nibble bits 0-2 pick one of the eight source bytes,
+// bit 3 replaces the byte by eight copies of its sign bit.
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+    uint32_t d;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+    return d;
+}
+__device__ __forceinline__ float lds_f32(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+    return v;
+}
+template <int IMM>
+__device__ __forceinline__ float lds_f32_imm(uint32_t addr) {
+    float v;
+    asm volatile("ld.shared.f32 %0, [%1+%2];" : "=f"(v) : "r"(addr), "n"(IMM));
+    return v;
+}
+template <int IMM>
+__device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
+    uint32_t v;
+    asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
+    return v;
+}
+__device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
+    asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
@@ -144,18 +175,14 @@ template <int Q, int NCW>
 struct TileCfg {
     static constexpr int CW = NCW * 32;             // columns per stage
     static constexpr int W_ROWS = KB_WORDS * Q;     // weight rows per stage
-    static constexpr int W_BYTES = W_ROWS * CW * 4;
-    static constexpr int A_ROWS = 2 * Q;            // alpha rows per stage (two groups at g = 128)
-    static constexpr int A_BYTES = A_ROWS * CW * 2;
-    static constexpr int STAGE_BYTES = W_BYTES + A_BYTES;
+    static constexpr int STAGE_BYTES = W_ROWS * CW * 4;
     static constexpr int THREADS = (NCW + 1) * 32;
 };
 
 // Builds the 32 tables of one K block.  Lane = chunk; a warp handles groups of
 // eight consecutive entries (entry >> 3 = hgrp).  Bank of every store = lane.
 template <int NCW>
-__device__ __forceinline__ void build_tables(const __half *__restrict__ xblk, unsigned char *lut_half, int warp,
-                                             int lane) {
+__device__ __forceinline__ void build_tables(const __half *__restrict__ xblk, uint32_t lut_half, int warp, int lane) {
     const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xblk) + lane);
     float xf[8];
     {
@@ -171,34 +198,47 @@ __device__ __forceinline__ void build_tables(const __half *__restrict__ xblk, un
 #pragma unroll
     for (int i = 0; i < 8; ++i)
         low[i] = ((i & 1) ? xf[0] : -xf[0]) + ((i & 2) ? xf[1] : -xf[1]) + ((i & 4) ? xf[2] : -xf[2]);
-    float *dst = reinterpret_cast<float *>(lut_half) + lane;
+    const uint32_t dst = lut_half + 4u * lane;
 #pragma unroll 1
     for (int hg = warp; hg < 32; hg += NCW) {
         const float hi = ((hg & 1) ? xf[3] : -xf[3]) + ((hg & 2) ? xf[4] : -xf[4]) + ((hg & 4) ? xf[5] : -xf[5]) +
                          ((hg & 8) ? xf[6] : -xf[6]) + ((hg & 16) ? xf[7] : -xf[7]);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) dst[(hg * 8 + i) * (LUT_ROW_BYTES / 4)] = hi + low[i];
+        for (int i = 0; i < 8; ++i) sts_f32(dst + (uint32_t)(hg * 8 + i) * LUT_ROW_BYTES, hi + low[i]);
     }
 }
 
-template <int Q, int NCW>
-__global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
+// Shared-window address at which the dynamic shared memory of a kernel without static
+// shared memory starts on sm_100 (the first KB of every CTA's allocation is reserved by the
+// driver).  The ABS variant of the kernel bakes the table address into the immediate field of
+// its lookups; it verifies the assumption at run time and reports SAL_E_UNSUPPORTED through
+// the status word instead of computing if it does not hold.
+constexpr uint32_t SMEM_DYNAMIC_BASE = 1024;
+
+template <int Q, int NCW, bool ABS>
+__global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
     lutgemv_tiled_kernel(const __grid_constant__ TileParams P) {
     using C = TileCfg<Q, NCW>;
     constexpr int CW = C::CW;
-    extern __shared__ __align__(1024) unsigned char smem[];
-    __shared__ int s_last;
+    extern __shared__ __align__(128) unsigned char smem[];
 
-    unsigned char *lut = smem;
     unsigned char *stage_base = smem + LUT_BYTES;
+    const uint32_t lut_s = smem_u32(smem);
+    const uint32_t stage_s = smem_u32(stage_base);
     const int stages = P.stages;
     uint64_t *bars = reinterpret_cast<uint64_t *>(stage_base + (size_t)stages * C::STAGE_BYTES);
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = smem_u32(bars + stages);
+    volatile int &s_last = *reinterpret_cast<volatile int *>(bars + 2 * stages);
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+
+    if (ABS && lut_s != SMEM_DYNAMIC_BASE) {  // uniform over the grid: everybody leaves
+        if (tid == 0 && P.status) atomicExch(P.status, SAL_E_UNSUPPORTED);
+        return;
+    }
 
     // which problem / column range / K split is this CTA
     int pi = 0;
@@ -214,7 +254,6 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
     const int nsub = min(pr.nsub_per_range, pr.nsub_total - sub_begin);
     const int kb_begin = (int)(((long long)split * pr.kblocks) / pr.splits);
     const int kb_end = (int)(((long long)(split + 1) * pr.kblocks) / pr.splits);
-    const int gpk = (pr.g == 128) ? 2 : 1;  // groups per K block
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -228,26 +267,26 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
 
     if (warp == NCW) {
         // ------------------------------ producer warp ------------------------------
-        int it = 0;
+        int st = 0;
+        uint32_t phase = 0;  // parity of the consumers' release being waited for (previous use of the stage)
+        bool first_round = true;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-            const int grp0 = (kb * KB_FEATS) / pr.g;
-            for (int sub = 0; sub < nsub; ++sub, ++it) {
-                const int st = it % stages;
-                const int use = it / stages;
-                if (use > 0) mbar_wait(empty0 + 8 * st, (use - 1) & 1, P.status);
+            for (int sub = 0; sub < nsub; ++sub) {
+                if (!first_round) mbar_wait(empty0 + 8 * st, phase, P.status);
                 const int n0 = (sub_begin + sub) * CW;
                 const int valid = min(CW, N - n0);
                 const uint32_t full = full0 + 8 * st;
-                unsigned char *sdst = stage_base + (size_t)st * C::STAGE_BYTES;
-                if (lane == 0) mbar_expect_tx(full, (uint32_t)(C::W_ROWS * valid * 4 + gpk * Q * valid * 2));
+                if (lane == 0) mbar_expect_tx(full, (uint32_t)(C::W_ROWS * valid * 4));
                 __syncwarp();
-                for (int row = lane; row < C::W_ROWS; row += 32) {
-                    const uint32_t *src = pr.bw + ((size_t)kb * C::W_ROWS + row) * N + n0;
-                    tma_bulk_g2s(smem_u32(sdst + (size_t)row * CW * 4), src, (uint32_t)valid * 4, full);
+                if (lane < C::W_ROWS) {
+                    const uint32_t *src = pr.bw + ((size_t)kb * C::W_ROWS + lane) * N + n0;
+                    tma_bulk_g2s(stage_s + (uint32_t)st * C::STAGE_BYTES + (uint32_t)lane * CW * 4, src,
+                                 (uint32_t)valid * 4, full);
                 }
-                for (int row = lane; row < gpk * Q; row += 32) {
-                    const __half *src = pr.alpha + ((size_t)grp0 * Q + row) * N + n0;
-                    tma_bulk_g2s(smem_u32(sdst + C::W_BYTES + (size_t)row * CW * 2), src, (uint32_t)valid * 2, full);
+                if (++st == stages) {
+                    st = 0;
+                    if (first_round) first_round = false;
+                    else phase ^= 1u;
                 }
             }
         }
@@ -259,43 +298,78 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
     const int hw = lane >> 4;
     const int rot = (lane >> 2) & 3;
     const int s4 = lane & 3;
+    // Lookup address = one byte-permute of (weight word, packed constants):
+    //   byte 0 <- 4*chunk (the bank), taken from byte t of cpack
+    //   byte 1 <- the weight byte (table entry index; one entry = one 256-byte row)
+    //   bytes 2,3 <- sign replication of a constant < 128, i.e. zero.
     unsigned sel[4];
-    unsigned coff[2][4][4];
+    unsigned cpack[2][4];
     unsigned wrow[2][4];
 #pragma unroll
-    for (int t = 0; t < 4; ++t) sel[t] = 4u | (unsigned)(((t + s4) & 3) << 4) | (6u << 8) | (7u << 12);
+    for (int t = 0; t < 4; ++t)
+        sel[t] = (unsigned)(4 + t) | (unsigned)(((t + s4) & 3) << 4) | (unsigned)((8 | (4 + t)) << 8) |
+                 (unsigned)((8 | (4 + t)) << 12);
 #pragma unroll
     for (int hp = 0; hp < 2; ++hp)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int wi = 4 * (hp ^ hw) + ((j + rot) & 3);
-            wrow[hp][j] = (unsigned)(wi * Q * CW + col);
+            wrow[hp][j] = stage_s + (unsigned)((wi * Q * CW + col) * 4);
+            unsigned pk = 0;
 #pragma unroll
-            for (int t = 0; t < 4; ++t) coff[hp][j][t] = (unsigned)(16 * wi + 4 * ((t + s4) & 3));
+            for (int t = 0; t < 4; ++t) pk |= (unsigned)(16 * wi + 4 * ((t + s4) & 3)) << (8 * t);
+            cpack[hp][j] = pk;
         }
 
     float acc[MAX_SUB];
 #pragma unroll
     for (int i = 0; i < MAX_SUB; ++i) acc[i] = 0.f;
 
+    // alpha for one tile: two group slots x Q planes, fetched one tile ahead.  Slot hp of a
+    // lane covers the words of group (hp ^ hw) of the K block (or the block's only group).
+    const int gshift = (pr.g == 128) ? 1 : 0;
+    const int gdiv = pr.g / 128;  // 128-feature units per group
+    const size_t a_plane = (size_t)N;
+    auto load_alpha = [&](int kb, int sub, __half(&dst)[2][Q]) {
+        const int n = (sub_begin + sub) * CW + col;
+        const bool ok = n < N;
+        const int g0 = gshift ? (2 * kb + hw) : (2 * kb) / gdiv;
+        const int g1 = gshift ? (2 * kb + (hw ^ 1)) : g0;
+        const __half *p0 = pr.alpha + (size_t)g0 * Q * a_plane + n;
+        const __half *p1 = pr.alpha + (size_t)g1 * Q * a_plane + n;
+#pragma unroll
+        for (int b = 0; b < Q; ++b) {
+            dst[0][b] = ok ? __ldg(p0 + b * a_plane) : __float2half(0.f);
+            dst[1][b] = ok ? __ldg(p1 + b * a_plane) : __float2half(0.f);
+        }
+    };
+    __half a_next[2][Q];
+    if (kb_begin < kb_end) load_alpha(kb_begin, 0, a_next);  // constants: legal before the dependency wait
+
     pdl_wait();  // activations, bias, y and the scratch buffer may be written by the previous kernel
 
-    int it = 0;
-    for (int kb = kb_begin; kb < kb_end; ++kb) {
-        const int par = (kb - kb_begin) & 1;
-        build_tables<NCW>(pr.x + (size_t)kb * KB_FEATS, lut + par * 128, warp, lane);
+    int st = 0;
+    uint32_t phase = 0;
+    // One K block: build its tables into half `PAR` of the table rows, then walk the column tiles.
+    auto process_block = [&](int kb, auto par_tag) {
+        constexpr int PAR = decltype(par_tag)::value;
+        build_tables<NCW>(pr.x + (size_t)kb * KB_FEATS, lut_s + PAR * 128, warp, lane);
         consumer_barrier(NCW * 32);
-        const unsigned char *lutp = lut + par * 128;
 #pragma unroll
         for (int sub = 0; sub < MAX_SUB; ++sub) {
             if (sub < nsub) {
-                const int st = it % stages;
-                const int use = it / stages;
-                ++it;
-                mbar_wait(full0 + 8 * st, use & 1, P.status);
-                const unsigned char *sdst = stage_base + (size_t)st * C::STAGE_BYTES;
-                const uint32_t *wst = reinterpret_cast<const uint32_t *>(sdst);
-                const __half *ast = reinterpret_cast<const __half *>(sdst + C::W_BYTES);
+                __half a_cur[2][Q];
+#pragma unroll
+                for (int hp = 0; hp < 2; ++hp)
+#pragma unroll
+                    for (int b = 0; b < Q; ++b) a_cur[hp][b] = a_next[hp][b];
+                {
+                    const bool more_sub = (sub + 1 < nsub);
+                    const int kb_n = more_sub ? kb : kb + 1;
+                    if (kb_n < kb_end) load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
+                }
+                mbar_wait(full0 + 8 * st, phase, P.status);
+                const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
                 float a_sub = 0.f;
 #pragma unroll
                 for (int hp = 0; hp < 2; ++hp) {
@@ -304,25 +378,38 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
                     for (int b = 0; b < Q; ++b) part[b] = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
+                        const uint32_t wr = wrow[hp][j] + soff;
 #pragma unroll
                         for (int b = 0; b < Q; ++b) {
-                            const uint32_t w = wst[wrow[hp][j] + b * CW];
+                            uint32_t w;
+                            if (b == 0) w = lds_u32_imm<0>(wr);
+                            else if (b == 1) w = lds_u32_imm<1 * CW * 4>(wr);
+                            else if (b == 2) w = lds_u32_imm<2 * CW * 4>(wr);
+                            else w = lds_u32_imm<3 * CW * 4>(wr);
 #pragma unroll
                             for (int t = 0; t < 4; ++t) {
-                                const unsigned addr = __byte_perm(w, coff[hp][j][t], sel[t]);
-                                part[b] += *reinterpret_cast<const float *>(lutp + addr);
+                                const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
+                                if (ABS) part[b] += lds_f32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off);
+                                else part[b] += lds_f32(off + lut_s + PAR * 128);
                             }
                         }
                     }
-                    const int gl = (gpk == 2) ? (hp ^ hw) : 0;
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) a_sub += __half2float(ast[(gl * Q + b) * CW + col]) * part[b];
+                    for (int b = 0; b < Q; ++b) a_sub += __half2float(a_cur[hp][b]) * part[b];
                 }
                 acc[sub] += a_sub;
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * st);
+                if (++st == stages) {
+                    st = 0;
+                    phase ^= 1u;
+                }
             }
         }
+    };
+    for (int kb = kb_begin; kb < kb_end; kb += 2) {
+        process_block(kb, std::integral_constant<int, 0>{});
+        if (kb + 1 < kb_end) process_block(kb + 1, std::integral_constant<int, 1>{});
     }
 
     // ---------------------------------- epilogue ----------------------------------
@@ -342,7 +429,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
 #pragma unroll
     for (int sub = 0; sub < MAX_SUB; ++sub) {
         const int n = (sub_begin + sub) * CW + col;
-        if (sub < nsub && n < N) pr.partials[(size_t)split * N + n] = acc[sub];
+        if (sub < nsub && n < N) __stcg(&pr.partials[(size_t)split * N + n], acc[sub]);
     }
     __threadfence();
     consumer_barrier(NCW * 32);
@@ -353,11 +440,21 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
     consumer_barrier(NCW * 32);
     if (s_last) {
         __threadfence();
+        // The last CTA of a column range to arrive sums the partials of all K splits in
+        // ascending split order (fixed, hence deterministic), 16 independent loads at a time.
+        const int S = pr.splits;
         for (int sub = 0; sub < nsub; ++sub) {
             const int n = (sub_begin + sub) * CW + col;
             if (n < N) {
                 float v = 0.f;
-                for (int s = 0; s < pr.splits; ++s) v += __ldcg(&pr.partials[(size_t)s * N + n]);
+                for (int s0 = 0; s0 < S; s0 += 16) {
+                    float t[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        t[i] = (s0 + i < S) ? __ldcg(&pr.partials[(size_t)(s0 + i) * N + n]) : 0.f;
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v += t[i];
+                }
                 if (pr.bias) v += __half2float(pr.bias[n]);
                 if (P.accumulate) v += __half2float(pr.y[n]);
                 pr.y[n] = __float2half_rn(v);
@@ -365,6 +462,12 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 1)
         }
         if (tid == 0) pr.counters[range] = 0u;  // leave the scratch buffer ready for the next call
     }
+}
+
+// Reports where dynamic shared memory starts for a kernel without static shared memory.
+__global__ void smem_base_probe_kernel(uint32_t *out) {
+    extern __shared__ __align__(128) unsigned char probe_smem[];
+    if (threadIdx.x == 0) *out = smem_u32(probe_smem);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -479,11 +582,18 @@ __global__ void __launch_bounds__(128) lutgemv_generic_kernel(const GenericParam
 // ------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------
+thread_local cudaError_t g_last_cuda_error = cudaSuccess;
+inline bool cuda_ok(cudaError_t e) {
+    if (e != cudaSuccess) g_last_cuda_error = e;
+    return e == cudaSuccess;
+}
+
 struct DeviceInfo {
     int valid;
     int sms;
     int cc_major;
     int smem_optin;
+    int smem_base;  // 0 = not probed yet, else the probed start of dynamic shared memory
 };
 DeviceInfo g_dev[64];
 
@@ -514,21 +624,26 @@ struct Plan {
     int ranges, splits, nsub_per_range, nsub_total, kblocks;
 };
 
-// Chooses column ranges x K splits for one problem given a CTA budget.
-Plan plan_problem(int K, int N, int cta_budget, bool allow_split) {
+// Chooses column ranges x K splits for one problem.  `sm_budget` is the number
+// of SMs this problem may count on; two CTAs are co-resident per SM and share
+// its shared-memory pipe, so the time of an SM is the sum of its CTAs' work.
+// Work unit = one 256-feature x 256-column tile; building the tables of one K
+// block costs about 0.45 units.
+Plan plan_problem(int K, int N, int sm_budget, bool allow_split) {
     Plan best{};
     const int nsub_total = (N + TILE_CW - 1) / TILE_CW;
     const int kblocks = K / KB_FEATS;
     double best_cost = 1e30;
     for (int per = 1; per <= MAX_SUB && per <= nsub_total; ++per) {
         const int ranges = (nsub_total + per - 1) / per;
-        int smax = allow_split ? (kblocks < MAX_SPLIT ? kblocks : MAX_SPLIT) : 1;
+        const int smax = allow_split ? (kblocks < MAX_SPLIT ? kblocks : MAX_SPLIT) : 1;
         for (int splits = 1; splits <= smax; ++splits) {
             const int ctas = ranges * splits;
             const int kb_per = (kblocks + splits - 1) / splits;
-            const int waves = (ctas + cta_budget - 1) / cta_budget;
-            // cost in "stage units": lookups + a table-build penalty per K block + a split penalty
-            const double cost = waves * (kb_per * (per + 0.45)) + 0.02 * splits;
+            const int per_sm = (ctas + sm_budget - 1) / sm_budget;  // CTAs an SM ends up running
+            double cost = per_sm * (kb_per * (per + 0.45));
+            if (per_sm > 2) cost += 2.0 * ((per_sm + 1) / 2 - 1);  // later waves restart the pipeline
+            cost += 0.02 * splits + (splits > 1 ? 0.5 + 0.15 * per * ((splits + 15) / 16) : 0.0);  // reduction tail
             if (cost < best_cost) {
                 best_cost = cost;
                 best = Plan{ranges, splits, per, nsub_total, kblocks};
@@ -551,22 +666,29 @@ int stage_bytes_for(int q) {
     }
 }
 
-int g_stage_override = 0;  // test/benchmark hook (sal_debug_set_stages)
+int g_stage_override = 0;  // measurement hooks (sal_debug_set)
+int g_budget_pct = 100;
 
+// Ring depth: as many stages as fit in half of an SM's shared memory next to the
+// 64 KB of tables, so that two CTAs (of this kernel or of the next one in the
+// stream) are resident together.
 int choose_stages(int q, int smem_optin, int *smem_bytes) {
     const int sb = stage_bytes_for(q);
-    int budget = smem_optin - LUT_BYTES - 256;
+    const int per_cta = (smem_optin + 1024) / 2 - 1024;  // each resident CTA also reserves 1 KB
+    int budget = per_cta - LUT_BYTES - 256;              // barriers and the reduction flag
     int stages = budget / sb;
     if (stages > 8) stages = 8;
     if (g_stage_override > 0 && g_stage_override < stages) stages = g_stage_override;
-    if (stages < 2) return 0;
-    *smem_bytes = LUT_BYTES + stages * sb + 2 * stages * 8;
+    if (stages < 1) return 0;
+    *smem_bytes = LUT_BYTES + stages * sb + 2 * stages * 8 + 16;
     return stages;
 }
 
-template <int Q>
-cudaError_t launch_tiled(const TileParams &P, int ctas, int smem, unsigned flags, cudaStream_t stream) {
-    auto kern = lutgemv_tiled_kernel<Q, TILE_NCW>;
+int g_abs_override = -1;  // measurement hook: 0/1 forces the addressing variant
+
+template <int Q, bool ABS>
+cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int smem, unsigned flags, cudaStream_t stream) {
+    auto kern = lutgemv_tiled_kernel<Q, TILE_NCW, ABS>;
     static int configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -588,6 +710,13 @@ cudaError_t launch_tiled(const TileParams &P, int ctas, int smem, unsigned flags
         cfg.numAttrs = 1;
     }
     return cudaLaunchKernelEx(&cfg, kern, P);
+}
+
+template <int Q>
+cudaError_t launch_tiled(const TileParams &P, int ctas, int smem, unsigned flags, bool abs_ok, cudaStream_t stream) {
+    const bool use_abs = g_abs_override >= 0 ? (g_abs_override != 0) : abs_ok;
+    return use_abs ? launch_tiled_variant<Q, true>(P, ctas, smem, flags, stream)
+                   : launch_tiled_variant<Q, false>(P, ctas, smem, flags, stream);
 }
 
 bool tiled_eligible(const void *bw, const void *alpha, const void *bias, const void *x, const void *y, int M, int K,
@@ -621,7 +750,7 @@ int run_generic(int kind, const GenericParams &p, cudaStream_t stream) {
         case B_U16: lutgemv_generic_kernel<B_U16><<<grid, 128, 0, stream>>>(p); break;
         default: lutgemv_generic_kernel<B_I8><<<grid, 128, 0, stream>>>(p); break;
     }
-    return cudaGetLastError() == cudaSuccess ? SAL_OK : SAL_E_LAUNCH;
+    return cuda_ok(cudaGetLastError()) ? SAL_OK : SAL_E_LAUNCH;
 }
 
 int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void *workspace, size_t ws_bytes,
@@ -655,7 +784,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     for (int i = 0; i < count; ++i) {
         const sal_problem &sp = problems[i];
         const double units = (double)((sp.N + TILE_CW - 1) / TILE_CW) * (sp.K / KB_FEATS);
-        int budget = (int)(sms * units / units_total + 0.5);
+        int budget = (int)(sms * (g_budget_pct / 100.0) * units / units_total + 0.5);
         if (budget < 1) budget = 1;
         Plan pl = plan_problem(sp.K, sp.N, budget, have_ws);
         TileProblem &tp = P.p[i];
@@ -693,14 +822,30 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         info_only->smem_bytes = smem;
         return SAL_OK;
     }
+    // The first call on a device that has a workspace probes where dynamic shared memory
+    // starts (one tiny kernel on `stream`, read back synchronously); it must therefore not be
+    // made under stream capture.  Until probed, the variant without baked-in addresses runs.
+    if (dev->smem_base == 0 && workspace != nullptr) {
+        uint32_t *slot = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(workspace) + 64);
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(stream, &cap);
+        if (cap == cudaStreamCaptureStatusNone) {
+            smem_base_probe_kernel<<<1, 32, 256, stream>>>(slot);
+            uint32_t base = 0;
+            if (cuda_ok(cudaMemcpyAsync(&base, slot, 4, cudaMemcpyDeviceToHost, stream)) &&
+                cuda_ok(cudaStreamSynchronize(stream)))
+                dev->smem_base = base ? (int)base : -1;
+        }
+    }
+    const bool abs_ok = dev->smem_base == (int)SMEM_DYNAMIC_BASE;
     cudaError_t e;
     switch (q) {
-        case 1: e = launch_tiled<1>(P, cta, smem, flags, stream); break;
-        case 2: e = launch_tiled<2>(P, cta, smem, flags, stream); break;
-        case 3: e = launch_tiled<3>(P, cta, smem, flags, stream); break;
-        default: e = launch_tiled<4>(P, cta, smem, flags, stream); break;
+        case 1: e = launch_tiled<1>(P, cta, smem, flags, abs_ok, stream); break;
+        case 2: e = launch_tiled<2>(P, cta, smem, flags, abs_ok, stream); break;
+        case 3: e = launch_tiled<3>(P, cta, smem, flags, abs_ok, stream); break;
+        default: e = launch_tiled<4>(P, cta, smem, flags, abs_ok, stream); break;
     }
-    return e == cudaSuccess ? SAL_OK : SAL_E_LAUNCH;
+    return cuda_ok(e) ? SAL_OK : SAL_E_LAUNCH;
 }
 
 }  // namespace
@@ -727,6 +872,8 @@ const char *sal_status_string(int status) {
     }
 }
 
+const char *sal_last_cuda_error(void) { return cudaGetErrorString(g_last_cuda_error); }
+
 int sal_device_ok(void) {
     DeviceInfo *d = nullptr;
     return device_info(&d);
@@ -750,8 +897,17 @@ int sal_workspace_status(void *workspace, void *stream) {
     return st;
 }
 
-int sal_debug_set_stages(int stages) {
-    g_stage_override = stages;
+int sal_debug_set(const char *key, int value) {
+    if (!key) return SAL_E_NULL;
+    const auto eq = [&](const char *k) {
+        const char *a = key;
+        while (*a && *a == *k) ++a, ++k;
+        return *a == *k;
+    };
+    if (eq("stages")) g_stage_override = value;
+    else if (eq("abs")) g_abs_override = value;
+    else if (eq("budget_pct")) g_budget_pct = value > 0 ? value : 100;
+    else return SAL_E_UNSUPPORTED;
     return SAL_OK;
 }
 
