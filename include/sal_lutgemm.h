@@ -160,7 +160,9 @@ int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_in
 /* Measurement hook, process-wide, not for production use.  Keys: "stages" caps the
  * depth of the shared-memory ring of the tiled kernel (0 = as deep as fits);
  * "budget_pct" scales the number of SMs the planner sizes its grid for
- * (100 = one CTA per SM's worth of work, 200 = two). */
+ * (100 = one CTA per SM, 200 = two, the default); "abs" 0/1 forces the table
+ * addressing variant; "ablate" bit0/1/2 skips alpha loads / table builds /
+ * lookups (results are then meaningless; used to time the parts). */
 int sal_debug_set(const char *key, int value);
 
 #ifdef __cplusplus

@@ -78,6 +78,7 @@ struct TileParams {
     int count;
     int stages;
     int accumulate;
+    int ablate;  // measurement only: bit0 skip alpha loads, bit1 skip table builds, bit2 skip lookups
     int *status;
 };
 
@@ -332,7 +333,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
     const size_t a_plane = (size_t)N;
     auto load_alpha = [&](int kb, int sub, __half(&dst)[2][Q]) {
         const int n = (sub_begin + sub) * CW + col;
-        const bool ok = n < N;
+        const bool ok = n < N && !(P.ablate & 1);
         const int g0 = gshift ? (2 * kb + hw) : (2 * kb) / gdiv;
         const int g1 = gshift ? (2 * kb + (hw ^ 1)) : g0;
         const __half *p0 = pr.alpha + (size_t)g0 * Q * a_plane + n;
@@ -353,11 +354,14 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
     // One K block: build its tables into half `PAR` of the table rows, then walk the column tiles.
     auto process_block = [&](int kb, auto par_tag) {
         constexpr int PAR = decltype(par_tag)::value;
-        build_tables<NCW>(pr.x + (size_t)kb * KB_FEATS, lut_s + PAR * 128, warp, lane);
+        if (!(P.ablate & 2)) build_tables<NCW>(pr.x + (size_t)kb * KB_FEATS, lut_s + PAR * 128, warp, lane);
         consumer_barrier(NCW * 32);
-#pragma unroll
-        for (int sub = 0; sub < MAX_SUB; ++sub) {
-            if (sub < nsub) {
+        // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
+        // unrolling it over the column tiles overflows the instruction cache.  acc[] is then
+        // indexed dynamically and lives in (L1-resident) local memory: two accesses per tile.
+#pragma unroll 1
+        for (int sub = 0; sub < nsub; ++sub) {
+            {
                 __half a_cur[2][Q];
 #pragma unroll
                 for (int hp = 0; hp < 2; ++hp)
@@ -371,11 +375,12 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
                 mbar_wait(full0 + 8 * st, phase, P.status);
                 const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
                 float a_sub = 0.f;
+                if (!(P.ablate & 4))
 #pragma unroll
                 for (int hp = 0; hp < 2; ++hp) {
-                    float part[Q];
+                    float part[Q], part2[Q];
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) part[b] = 0.f;
+                    for (int b = 0; b < Q; ++b) part[b] = part2[b] = 0.f;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const uint32_t wr = wrow[hp][j] + soff;
@@ -389,13 +394,15 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
 #pragma unroll
                             for (int t = 0; t < 4; ++t) {
                                 const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
-                                if (ABS) part[b] += lds_f32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off);
-                                else part[b] += lds_f32(off + lut_s + PAR * 128);
+                                const float e = ABS ? lds_f32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off)
+                                                    : lds_f32(off + lut_s + PAR * 128);
+                                if (t & 1) part2[b] += e;
+                                else part[b] += e;
                             }
                         }
                     }
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) a_sub += __half2float(a_cur[hp][b]) * part[b];
+                    for (int b = 0; b < Q; ++b) a_sub += __half2float(a_cur[hp][b]) * (part[b] + part2[b]);
                 }
                 acc[sub] += a_sub;
                 __syncwarp();
@@ -667,7 +674,8 @@ int stage_bytes_for(int q) {
 }
 
 int g_stage_override = 0;  // measurement hooks (sal_debug_set)
-int g_budget_pct = 100;
+int g_budget_pct = 200;  // two co-resident CTAs per SM
+int g_ablate = 0;
 
 // Ring depth: as many stages as fit in half of an SM's shared memory next to the
 // 64 KB of tables, so that two CTAs (of this kernel or of the next one in the
@@ -771,6 +779,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     P.count = count;
     P.stages = stages;
     P.accumulate = (flags & SAL_ACCUMULATE) ? 1 : 0;
+    P.ablate = g_ablate;
     P.status = workspace ? reinterpret_cast<int *>(workspace) : nullptr;
 
     // CTA budget per problem, proportional to its weight volume
@@ -906,6 +915,7 @@ int sal_debug_set(const char *key, int value) {
     };
     if (eq("stages")) g_stage_override = value;
     else if (eq("abs")) g_abs_override = value;
+    else if (eq("ablate")) g_ablate = value;
     else if (eq("budget_pct")) g_budget_pct = value > 0 ? value : 100;
     else return SAL_E_UNSUPPORTED;
     return SAL_OK;

@@ -1,0 +1,80 @@
+"""The C-ABI shared library: it loads, exports every symbol the header declares,
+plans launches and validates arguments without needing a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from shiftaddllm_b200 import _lib
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_functions():
+    text = open(os.path.join(REPO, "include", "sal_lutgemm.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sal_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_exports_every_declared_symbol(lib):
+    names = declared_functions()
+    assert len(names) >= 14
+    for name in names:
+        assert hasattr(lib, name), f"{name} is declared in include/sal_lutgemm.h but not exported"
+    # and the ctypes table covers exactly the header
+    assert sorted(_lib.SIGNATURES) == names
+
+
+def test_version_and_strings(lib):
+    assert lib.sal_version() == 100
+    assert _lib.status_string(0) == "ok"
+    assert "workspace" in _lib.status_string(_lib.SAL_E_WORKSPACE)
+    assert lib.sal_workspace_bytes(1, 4096) == 16384 + 4096 * 64 * 4
+
+
+def test_planner_without_gpu(lib):
+    info = _lib.SalPlanInfo()
+    assert lib.sal_plan_shift_scale(1, 4096, 4096, 3, 32, ctypes.byref(info)) == 0
+    assert info.tiled == 1 and info.ranges * info.splits == info.ctas and info.stages >= 2
+    assert info.smem_bytes <= 115712            # two CTAs must fit one SM
+    assert lib.sal_plan_shift_scale(1, 4096, 4096, 3, 128, ctypes.byref(info)) == 0   # g = 32
+    assert info.tiled == 0
+    assert lib.sal_plan_shift_scale(4, 4096, 4096, 3, 32, ctypes.byref(info)) == 0    # M > 1
+    assert info.tiled == 0
+    assert lib.sal_plan_shift_scale(1, 100, 64, 3, 1, ctypes.byref(info)) == _lib.SAL_E_SHAPE
+    for k, n, q in ((4096, 11008, 3), (11008, 4096, 3), (8192, 28672, 2), (28672, 8192, 2), (8192, 1024, 2), (768, 768, 3)):
+        assert lib.sal_plan_shift_scale(1, k, n, q, k // 128, ctypes.byref(info)) == 0
+        assert info.tiled == 1 and 1 <= info.splits <= 64 and info.ctas >= 1
+
+
+def test_argument_validation_happens_before_any_gpu_work(lib):
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.addressof(buf)
+    p = (p + 15) & ~15
+    call = lib.sal_lutgemv_shift_scale
+    assert call(None, p, None, p, p, 1, 256, 64, 3, 2, 0, None, 0, None) == _lib.SAL_E_NULL
+    assert call(p, p, None, p, p, 1, 250, 64, 3, 2, 0, None, 0, None) == _lib.SAL_E_SHAPE      # K % 32
+    assert call(p, p, None, p, p, 1, 256, 64, 9, 2, 0, None, 0, None) == _lib.SAL_E_SHAPE      # q > 8
+    assert call(p, p, None, p, p, 65, 256, 64, 3, 2, 0, None, 0, None) == _lib.SAL_E_SHAPE     # M > 64
+    assert call(p, p, None, p, p, 1, 256, 64, 3, 3, 0, None, 0, None) == _lib.SAL_E_SHAPE      # K % groups
+    assert call(p + 2, p, None, p, p, 1, 256, 64, 3, 2, 0, None, 0, None) == _lib.SAL_E_ALIGN
+    assert lib.sal_lutgemm_block(p, p, None, p, p, 1, 256, 64, 3, 5, 0, None, 0, None) == _lib.SAL_E_SHAPE  # N % groups
+    assert lib.sal_lutgemv_grouped(None, 1, 0, None, 0, None) == _lib.SAL_E_NULL
+    probs = (_lib.SalProblem * 1)()
+    assert lib.sal_lutgemv_grouped(probs, 0, 0, None, 0, None) == _lib.SAL_E_SHAPE
+    assert lib.sal_lutgemv_grouped(probs, 9, 0, None, 0, None) == _lib.SAL_E_SHAPE
+    assert lib.sal_debug_set(b"no-such-key", 1) == _lib.SAL_E_UNSUPPORTED
+
+
+def test_no_cpu_fallback(lib):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    buf = ctypes.create_string_buffer(1 << 16)
+    p = (ctypes.addressof(buf) + 255) & ~255
+    # well-formed arguments, but no device: the library must refuse, not compute on the host
+    rc = lib.sal_lutgemv_shift_scale(p, p, None, p, p, 1, 256, 64, 3, 2, 0, None, 0, None)
+    assert rc == _lib.SAL_E_DEVICE
+    assert lib.sal_device_ok() == _lib.SAL_E_DEVICE
