@@ -256,14 +256,16 @@ def run_ours(args, rank, world, device):
 
 
 def read_traffic():
-    """Per-launch DRAM traffic (bytes) of the dominant kernel from the committed ncu summary, if any."""
-    path = os.path.join(REPO, "profiles", "traffic.json")
-    if os.path.exists(path):
-        try:
-            return json.load(open(path)).get("dram_bytes_per_launch_scaled")
-        except Exception:  # noqa: BLE001
-            return None
-    return None
+    """Per-launch DRAM traffic (bytes) of the dominant kernel, taken from the committed ncu summary
+    (dram__bytes_read.sum + dram__bytes_write.sum, mean over the launch types of a decoder block)."""
+    import re
+
+    path = os.path.join(REPO, "profiles", "lutgemv_tiled_q3_decoder_block_full.md")
+    try:
+        m = re.search(r"Mean traffic per launch ([0-9 ]+) B", open(path).read())
+        return int(m.group(1).replace(" ", "")) if m else None
+    except OSError:
+        return None
 
 
 # ------------------------------------------------------------------------------------------
