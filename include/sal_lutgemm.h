@@ -93,6 +93,26 @@ int sal_lutgemv_shift_scale(const void *bw, const void *alpha, const void *bias,
                             void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * sal_lutgemv_shift_scale without a caller-supplied workspace and without any allocation.
+ * This entry has no counterpart in the reference.  It is for hosts that must not allocate device
+ * memory once they are running: a serving process whose memory pool already owns the whole GPU, a
+ * plugin called inside somebody else's stream capture (where cudaMalloc is illegal), an embedder
+ * that was given a fixed budget at start-up.  The split-K scratch is a fixed array inside the
+ * library image (about 4 MB per GPU that loads the library, held until the process exits), which
+ * bounds the problem size: M * N <= 16384, otherwise SAL_E_WORKSPACE is returned and nothing runs.
+ * Same arguments, results and flags as sal_lutgemv_shift_scale.
+ *  - The first call on each device looks up the array's device address and, for shapes that use
+ *    the tiled kernel, runs a one-off probe that synchronises the stream: make that first call
+ *    outside any stream capture.
+ *  - Every call uses the SAME array and first clears its status word and counters on `stream`.
+ *    Calls that can overlap on the GPU (different streams, or one stream with concurrent graph
+ *    branches) race on it and give wrong results: keep them ordered, or use the workspace entry.
+ *  - It calls no cudaMalloc/cudaFree and no allocating library routine.
+ */
+int sal_lutgemv_shift_scale_static(const void *bw, const void *alpha, const void *bias, const void *x, void *y,
+                                   int M, int K, int N, int q, int num_groups, unsigned flags, void *stream);
+
+/*
  * One alpha per (group, column), halved for each successive plane, plus an
  * offset term q_bias[g][n] * sum_{k in g} x[k].  alpha, q_bias fp16 [num_groups][N].
  * Replaces lutgemm_compute (lutgemm_cuda.cpp:88-98 -> lutgemm_cuda_kernel.cu:288-316

@@ -41,6 +41,7 @@ SIGNATURES = {
     "sal_workspace_bytes": (_sz, [_i, _i]),
     "sal_workspace_status": (_i, [_vp, _vp]),
     "sal_lutgemv_shift_scale": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
+    "sal_lutgemv_shift_scale_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp]),
     "sal_lutgemv_compute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemm_block": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemm_block_shift": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),

@@ -1062,4 +1062,33 @@ int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags, 
                            nullptr);
 }
 
+// ---- entry point that allocates nothing ---------------------------------------------------
+// Scratch for sal_lutgemv_shift_scale_static: lives in the library's own device image, so every
+// GPU that loads the library carries these ~4 MB until the process exits.
+#define SAL_STATIC_MAX_COLUMNS 16384
+static __device__ __align__(256) unsigned char g_static_scratch[WS_PARTIAL_OFFSET +
+                                                                (size_t)SAL_STATIC_MAX_COLUMNS * MAX_SPLIT * sizeof(float)];
+static void *g_static_scratch_addr[64];  // device address of the array above, per device ordinal
+
+int sal_lutgemv_shift_scale_static(const void *bw, const void *alpha, const void *bias, const void *x, void *y, int M,
+                                   int K, int N, int q, int num_groups, unsigned flags, void *stream) {
+    if (M < 1 || N < 1) return SAL_E_SHAPE;
+    if ((long long)M * (long long)N > SAL_STATIC_MAX_COLUMNS) return SAL_E_WORKSPACE;  // beyond the built-in scratch
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev)) || dev < 0 || dev >= 64) return SAL_E_DEVICE;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // `g_static_scratch` names a host-side stand-in here; the device address has to be asked for,
+        // with the device it is wanted for current (it is: cudaGetDevice above).
+        void *addr = nullptr;
+        if (!cuda_ok(cudaGetSymbolAddress(&addr, g_static_scratch)) || addr == nullptr) return SAL_E_LAUNCH;
+        g_static_scratch_addr[dev] = addr;
+    }
+    void *ws = g_static_scratch_addr[dev];
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left: the status word and the arrival counters
+    // must start at zero (a call that was cut short could have left counters half way).
+    if (!cuda_ok(cudaMemsetAsync(ws, 0, WS_PARTIAL_OFFSET, s))) return SAL_E_LAUNCH;
+    return sal_lutgemv_shift_scale(bw, alpha, bias, x, y, M, K, N, q, num_groups, flags, ws, sizeof(g_static_scratch), s);
+}
+
 }  // extern "C"
