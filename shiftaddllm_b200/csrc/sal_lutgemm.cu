@@ -8,9 +8,9 @@
 // once and never dequantised.
 //
 // Tiled kernel (M = 1, mode A), per CTA:
-//   * one producer warp issues TMA bulk copies (cp.async.bulk + mbarrier
-//     complete_tx) of [8 words][q planes][CW columns] weight tiles into a
-//     shared-memory ring.  The copies do not depend on the activations, so
+//   * one producer thread issues tiled TMA copies (cp.async.bulk.tensor.2d through a
+//     tensor map of the packed planes, completion on mbarrier transaction counts) of
+//     [8 words x q planes][256 columns] boxes into a shared-memory ring.  The copies do not depend on the activations, so
 //     under programmatic dependent launch they are issued before
 //     griddepcontrol.wait and overlap the previous kernel's tail.  A CTA uses
 //     at most half of an SM's shared memory, so the CTAs of two consecutive
@@ -31,6 +31,7 @@
 // Every wait on an mbarrier is bounded; on expiry the kernel records
 // SAL_E_TIMEOUT in the workspace header and carries on to its exit.
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -54,6 +55,7 @@ constexpr int WS_HEADER_BYTES = 256;
 constexpr int WS_COUNTER_BYTES = 16384 - WS_HEADER_BYTES;
 constexpr int WS_MAX_COUNTERS = WS_COUNTER_BYTES / 4;
 constexpr size_t WS_PARTIAL_OFFSET = 16384;
+constexpr int BOX_COLS = 256;             // columns of one TMA box (the limit of a tensor-map box dimension)
 
 struct TileProblem {
     const uint32_t *bw;
@@ -74,6 +76,9 @@ struct TileProblem {
 };
 
 struct TileParams {
+    // One tiled-TMA descriptor per problem: the packed planes seen as a 2-D uint32 tensor
+    // [rows = (K/32)*q][columns = N], box = [8*q rows][256 columns] = one ring stage.
+    alignas(64) CUtensorMap tmap[SAL_MAX_GROUP];
     TileProblem p[SAL_MAX_GROUP];
     int count;
     int stages;
@@ -127,12 +132,6 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, int *st
         }
     }
 }
-__device__ __forceinline__ void tma_bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-        "l"(src), "r"(bytes), "r"(bar)
-        : "memory");
-}
 // prmt.b32, generic mode: selector nibble bits 0-2 pick one of the eight source bytes,
 // bit 3 replaces the byte by eight copies of its sign bit.
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
@@ -159,6 +158,14 @@ __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
 }
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// Tiled TMA load of one 2-D box (no multicast).  x is the innermost (column) coordinate in
+// elements and must keep x * 4 bytes a multiple of 16; y is the row coordinate.
+__device__ __forceinline__ void tma_tile_2d_g2s(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() {
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -217,7 +224,7 @@ __device__ __forceinline__ void build_tables(const __half *__restrict__ xblk, ui
 constexpr uint32_t SMEM_DYNAMIC_BASE = 1024;
 
 template <int Q, int NCW, bool ABS>
-__global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
+__global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     lutgemv_tiled_kernel(const __grid_constant__ TileParams P) {
     using C = TileCfg<Q, NCW>;
     constexpr int CW = C::CW;
@@ -275,15 +282,16 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
             for (int sub = 0; sub < nsub; ++sub) {
                 if (!first_round) mbar_wait(empty0 + 8 * st, phase, P.status);
                 const int n0 = (sub_begin + sub) * CW;
-                const int valid = min(CW, N - n0);
                 const uint32_t full = full0 + 8 * st;
-                if (lane == 0) mbar_expect_tx(full, (uint32_t)(C::W_ROWS * valid * 4));
-                __syncwarp();
-                if (lane < C::W_ROWS) {
-                    const uint32_t *src = pr.bw + ((size_t)kb * C::W_ROWS + lane) * N + n0;
-                    tma_bulk_g2s(stage_s + (uint32_t)st * C::STAGE_BYTES + (uint32_t)lane * CW * 4, src,
-                                 (uint32_t)valid * 4, full);
+                if (lane == 0) {
+                    // columns past N are zero-filled by the TMA unit and still counted
+                    mbar_expect_tx(full, (uint32_t)C::STAGE_BYTES);
+#pragma unroll
+                    for (int bx = 0; bx < CW / BOX_COLS; ++bx)
+                        tma_tile_2d_g2s(stage_s + (uint32_t)st * C::STAGE_BYTES + (uint32_t)bx * (C::W_ROWS * BOX_COLS * 4),
+                                        &P.tmap[pi], n0 + bx * BOX_COLS, kb * C::W_ROWS, full);
                 }
+                __syncwarp();
                 if (++st == stages) {
                     st = 0;
                     if (first_round) first_round = false;
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int wi = 4 * (hp ^ hw) + ((j + rot) & 3);
-            wrow[hp][j] = stage_s + (unsigned)((wi * Q * CW + col) * 4);
+            wrow[hp][j] = stage_s + (unsigned)(((col / BOX_COLS) * (C::W_ROWS * BOX_COLS) + wi * Q * BOX_COLS + (col % BOX_COLS)) * 4);
             unsigned pk = 0;
 #pragma unroll
             for (int t = 0; t < 4; ++t) pk |= (unsigned)(16 * wi + 4 * ((t + s4) & 3)) << (8 * t);
@@ -388,9 +396,9 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
                         for (int b = 0; b < Q; ++b) {
                             uint32_t w;
                             if (b == 0) w = lds_u32_imm<0>(wr);
-                            else if (b == 1) w = lds_u32_imm<1 * CW * 4>(wr);
-                            else if (b == 2) w = lds_u32_imm<2 * CW * 4>(wr);
-                            else w = lds_u32_imm<3 * CW * 4>(wr);
+                            else if (b == 1) w = lds_u32_imm<1 * BOX_COLS * 4>(wr);
+                            else if (b == 2) w = lds_u32_imm<2 * BOX_COLS * 4>(wr);
+                            else w = lds_u32_imm<3 * BOX_COLS * 4>(wr);
 #pragma unroll
                             for (int t = 0; t < 4; ++t) {
                                 const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
@@ -448,23 +456,36 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, 2)
     if (s_last) {
         __threadfence();
         // The last CTA of a column range to arrive sums the partials of all K splits in
-        // ascending split order (fixed, hence deterministic), 16 independent loads at a time.
+        // ascending split order (fixed, hence deterministic).  Up to 4 column tiles x 16 splits
+        // = 64 independent L2 loads are in flight per thread, so the whole reduction costs one
+        // or two round trips instead of one per column tile.
         const int S = pr.splits;
-        for (int sub = 0; sub < nsub; ++sub) {
-            const int n = (sub_begin + sub) * CW + col;
-            if (n < N) {
-                float v = 0.f;
-                for (int s0 = 0; s0 < S; s0 += 16) {
-                    float t[16];
+        for (int sub0 = 0; sub0 < nsub; sub0 += 4) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int s0 = 0; s0 < S; s0 += 16) {
+                float t[4][16];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int n = (sub_begin + sub0 + u) * CW + col;
+                    const bool live = (sub0 + u < nsub) && (n < N);
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
-                        t[i] = (s0 + i < S) ? __ldcg(&pr.partials[(size_t)(s0 + i) * N + n]) : 0.f;
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v += t[i];
+                        t[u][i] = (live && s0 + i < S) ? __ldcg(&pr.partials[(size_t)(s0 + i) * N + n]) : 0.f;
                 }
-                if (pr.bias) v += __half2float(pr.bias[n]);
-                if (P.accumulate) v += __half2float(pr.y[n]);
-                pr.y[n] = __float2half_rn(v);
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[u] += t[u][i];
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int n = (sub_begin + sub0 + u) * CW + col;
+                if (sub0 + u < nsub && n < N) {
+                    float r = v[u];
+                    if (pr.bias) r += __half2float(pr.bias[n]);
+                    if (P.accumulate) r += __half2float(pr.y[n]);
+                    pr.y[n] = __float2half_rn(r);
+                }
             }
         }
         if (tid == 0) pr.counters[range] = 0u;  // leave the scratch buffer ready for the next call
@@ -624,21 +645,18 @@ int device_info(DeviceInfo **out) {
 
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
-constexpr int TILE_NCW = 8;
-constexpr int TILE_CW = TILE_NCW * 32;
 
 struct Plan {
     int ranges, splits, nsub_per_range, nsub_total, kblocks;
 };
 
-// Chooses column ranges x K splits for one problem.  `sm_budget` is the number
-// of SMs this problem may count on; two CTAs are co-resident per SM and share
-// its shared-memory pipe, so the time of an SM is the sum of its CTAs' work.
-// Work unit = one 256-feature x 256-column tile; building the tables of one K
-// block costs about 0.45 units.
-Plan plan_problem(int K, int N, int sm_budget, bool allow_split) {
+// Chooses column ranges x K splits for one problem.  `slots` is the number of CTAs of this
+// problem that can be resident at once (its share of SMs x CTAs per SM).  Work unit = one
+// 256-feature K block x one column tile; building the tables of a K block costs about 0.45
+// units; CTAs beyond `slots` run as later waves and restart the pipeline.
+Plan plan_problem(int K, int N, int slots, bool allow_split, int cw) {
     Plan best{};
-    const int nsub_total = (N + TILE_CW - 1) / TILE_CW;
+    const int nsub_total = (N + cw - 1) / cw;
     const int kblocks = K / KB_FEATS;
     double best_cost = 1e30;
     for (int per = 1; per <= MAX_SUB && per <= nsub_total; ++per) {
@@ -647,10 +665,9 @@ Plan plan_problem(int K, int N, int sm_budget, bool allow_split) {
         for (int splits = 1; splits <= smax; ++splits) {
             const int ctas = ranges * splits;
             const int kb_per = (kblocks + splits - 1) / splits;
-            const int per_sm = (ctas + sm_budget - 1) / sm_budget;  // CTAs an SM ends up running
-            double cost = per_sm * (kb_per * (per + 0.45));
-            if (per_sm > 2) cost += 2.0 * ((per_sm + 1) / 2 - 1);  // later waves restart the pipeline
-            cost += 0.02 * splits + (splits > 1 ? 0.5 + 0.15 * per * ((splits + 15) / 16) : 0.0);  // reduction tail
+            const int waves = (ctas + slots - 1) / slots;
+            double cost = waves * (kb_per * (per + 0.45)) + 2.0 * (waves - 1);
+            cost += 0.02 * splits + (splits > 1 ? 0.5 + 0.15 * ((per + 3) / 4) * ((splits + 15) / 16) : 0.0);  // reduction tail
             if (cost < best_cost) {
                 best_cost = cost;
                 best = Plan{ranges, splits, per, nsub_total, kblocks};
@@ -660,29 +677,22 @@ Plan plan_problem(int K, int N, int sm_budget, bool allow_split) {
     return best;
 }
 
-template <int Q>
-int tile_stage_bytes() {
-    return TileCfg<Q, TILE_NCW>::STAGE_BYTES;
-}
-int stage_bytes_for(int q) {
-    switch (q) {
-        case 1: return tile_stage_bytes<1>();
-        case 2: return tile_stage_bytes<2>();
-        case 3: return tile_stage_bytes<3>();
-        default: return tile_stage_bytes<4>();
-    }
-}
+int stage_bytes_for(int q, int ncw) { return KB_WORDS * q * ncw * 32 * 4; }
 
 int g_stage_override = 0;  // measurement hooks (sal_debug_set)
-int g_budget_pct = 200;  // two co-resident CTAs per SM
+int g_budget_pct = 0;  // 0 = as many CTAs as can be resident (CTAs per SM x 100 %)
 int g_ablate = 0;
+int g_full_sm = 0;  // measurement hook: let one CTA use a whole SM's shared memory (deeper ring, one CTA per SM)
 
 // Ring depth: as many stages as fit in half of an SM's shared memory next to the
 // 64 KB of tables, so that two CTAs (of this kernel or of the next one in the
 // stream) are resident together.
-int choose_stages(int q, int smem_optin, int *smem_bytes) {
-    const int sb = stage_bytes_for(q);
-    const int per_cta = (smem_optin + 1024) / 2 - 1024;  // each resident CTA also reserves 1 KB
+int g_ncw = 8;  // consumer warps per CTA: 8 (two CTAs per SM) or 16 (one CTA per SM, whole shared memory)
+
+int choose_stages(int q, int ncw, int smem_optin, int *smem_bytes) {
+    const int sb = stage_bytes_for(q, ncw);
+    const bool whole_sm = g_full_sm || ncw > 8;
+    const int per_cta = whole_sm ? smem_optin : (smem_optin + 1024) / 2 - 1024;  // each resident CTA also reserves 1 KB
     int budget = per_cta - LUT_BYTES - 256;              // barriers and the reduction flag
     int stages = budget / sb;
     if (stages > 8) stages = 8;
@@ -694,9 +704,36 @@ int choose_stages(int q, int smem_optin, int *smem_bytes) {
 
 int g_abs_override = -1;  // measurement hook: 0/1 forces the addressing variant
 
-template <int Q, bool ABS>
+// cuTensorMapEncodeTiled is a driver entry point; it is looked up through the runtime so that the
+// library does not link against libcuda.
+typedef CUresult (*TensorMapEncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                           const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                           CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                           CUtensorMapFloatOOBfill);
+TensorMapEncodeTiledFn g_encode_tiled = nullptr;
+
+int encode_weight_map(CUtensorMap *out, const void *bw, int K, int N, int q) {
+    if (!g_encode_tiled) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (!cuda_ok(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres)) ||
+            qres != cudaDriverEntryPointSuccess || fn == nullptr)
+            return SAL_E_LAUNCH;
+        g_encode_tiled = reinterpret_cast<TensorMapEncodeTiledFn>(fn);
+    }
+    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 32) * (cuuint64_t)q};
+    const cuuint64_t strides[1] = {(cuuint64_t)N * 4};  // bytes between rows; N % 4 == 0 keeps it a multiple of 16
+    const cuuint32_t box[2] = {(cuuint32_t)BOX_COLS, (cuuint32_t)(KB_WORDS * q)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = g_encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(bw), dims, strides, box,
+                                      estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? SAL_OK : SAL_E_LAUNCH;
+}
+
+template <int Q, int NCW, bool ABS>
 cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int smem, unsigned flags, cudaStream_t stream) {
-    auto kern = lutgemv_tiled_kernel<Q, TILE_NCW, ABS>;
+    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS>;
     static int configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -707,7 +744,7 @@ cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int smem, unsign
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)ctas);
-    cfg.blockDim = dim3(TileCfg<Q, TILE_NCW>::THREADS);
+    cfg.blockDim = dim3(TileCfg<Q, NCW>::THREADS);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[1];
@@ -721,10 +758,13 @@ cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int smem, unsign
 }
 
 template <int Q>
-cudaError_t launch_tiled(const TileParams &P, int ctas, int smem, unsigned flags, bool abs_ok, cudaStream_t stream) {
+cudaError_t launch_tiled(const TileParams &P, int ncw, int ctas, int smem, unsigned flags, bool abs_ok, cudaStream_t stream) {
     const bool use_abs = g_abs_override >= 0 ? (g_abs_override != 0) : abs_ok;
-    return use_abs ? launch_tiled_variant<Q, true>(P, ctas, smem, flags, stream)
-                   : launch_tiled_variant<Q, false>(P, ctas, smem, flags, stream);
+    if (ncw > 8)
+        return use_abs ? launch_tiled_variant<Q, 16, true>(P, ctas, smem, flags, stream)
+                       : launch_tiled_variant<Q, 16, false>(P, ctas, smem, flags, stream);
+    return use_abs ? launch_tiled_variant<Q, 8, true>(P, ctas, smem, flags, stream)
+                   : launch_tiled_variant<Q, 8, false>(P, ctas, smem, flags, stream);
 }
 
 bool tiled_eligible(const void *bw, const void *alpha, const void *bias, const void *x, const void *y, int M, int K,
@@ -772,7 +812,10 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const int optin = dev ? dev->smem_optin : 232448;
     const int q = problems[0].q;
     int smem = 0;
-    const int stages = choose_stages(q, optin, &smem);
+    const int ncw = g_ncw > 8 ? 16 : 8;
+    const int cw = ncw * 32;
+    const int ctas_per_sm = ncw > 8 ? 1 : 2;
+    const int stages = choose_stages(q, ncw, optin, &smem);
     if (stages == 0) return SAL_E_UNSUPPORTED;
 
     TileParams P = {};
@@ -785,17 +828,18 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     // CTA budget per problem, proportional to its weight volume
     double units_total = 0;
     for (int i = 0; i < count; ++i)
-        units_total += (double)((problems[i].N + TILE_CW - 1) / TILE_CW) * (problems[i].K / KB_FEATS);
+        units_total += (double)((problems[i].N + cw - 1) / cw) * (problems[i].K / KB_FEATS);
     int cta = 0;
     int counter_off = 0;
     size_t n_off = 0;
     const bool have_ws = workspace != nullptr && ws_bytes >= WS_PARTIAL_OFFSET;
     for (int i = 0; i < count; ++i) {
         const sal_problem &sp = problems[i];
-        const double units = (double)((sp.N + TILE_CW - 1) / TILE_CW) * (sp.K / KB_FEATS);
-        int budget = (int)(sms * (g_budget_pct / 100.0) * units / units_total + 0.5);
+        const double units = (double)((sp.N + cw - 1) / cw) * (sp.K / KB_FEATS);
+        const int pct = g_budget_pct > 0 ? g_budget_pct : 100 * ctas_per_sm;
+        int budget = (int)(sms * (pct / 100.0) * units / units_total + 0.5);
         if (budget < 1) budget = 1;
-        Plan pl = plan_problem(sp.K, sp.N, budget, have_ws);
+        Plan pl = plan_problem(sp.K, sp.N, budget, have_ws, cw);
         TileProblem &tp = P.p[i];
         tp.bw = reinterpret_cast<const uint32_t *>(sp.bw);
         tp.alpha = reinterpret_cast<const __half *>(sp.alpha);
@@ -811,6 +855,10 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         tp.ranges = pl.ranges;
         tp.splits = pl.splits;
         tp.cta_begin = cta;
+        if (!info_only) {
+            const int erc = encode_weight_map(&P.tmap[i], sp.bw, sp.K, sp.N, sp.q);
+            if (erc != SAL_OK) return erc;
+        }
         if (pl.splits > 1) {
             if (counter_off + pl.ranges > WS_MAX_COUNTERS) return SAL_E_WORKSPACE;
             const size_t need = WS_PARTIAL_OFFSET + (n_off + (size_t)sp.N) * MAX_SPLIT * sizeof(float);
@@ -849,10 +897,10 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const bool abs_ok = dev->smem_base == (int)SMEM_DYNAMIC_BASE;
     cudaError_t e;
     switch (q) {
-        case 1: e = launch_tiled<1>(P, cta, smem, flags, abs_ok, stream); break;
-        case 2: e = launch_tiled<2>(P, cta, smem, flags, abs_ok, stream); break;
-        case 3: e = launch_tiled<3>(P, cta, smem, flags, abs_ok, stream); break;
-        default: e = launch_tiled<4>(P, cta, smem, flags, abs_ok, stream); break;
+        case 1: e = launch_tiled<1>(P, ncw, cta, smem, flags, abs_ok, stream); break;
+        case 2: e = launch_tiled<2>(P, ncw, cta, smem, flags, abs_ok, stream); break;
+        case 3: e = launch_tiled<3>(P, ncw, cta, smem, flags, abs_ok, stream); break;
+        default: e = launch_tiled<4>(P, ncw, cta, smem, flags, abs_ok, stream); break;
     }
     return cuda_ok(e) ? SAL_OK : SAL_E_LAUNCH;
 }
@@ -916,7 +964,9 @@ int sal_debug_set(const char *key, int value) {
     if (eq("stages")) g_stage_override = value;
     else if (eq("abs")) g_abs_override = value;
     else if (eq("ablate")) g_ablate = value;
-    else if (eq("budget_pct")) g_budget_pct = value > 0 ? value : 100;
+    else if (eq("full_sm")) g_full_sm = value;
+    else if (eq("ncw")) g_ncw = value;
+    else if (eq("budget_pct")) g_budget_pct = value > 0 ? value : 0;
     else return SAL_E_UNSUPPORTED;
     return SAL_OK;
 }
