@@ -334,26 +334,29 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
 #pragma unroll
     for (int i = 0; i < MAX_SUB; ++i) acc[i] = 0.f;
 
-    // alpha for one tile: two group slots x Q planes, fetched one tile ahead.  Slot hp of a
-    // lane covers the words of group (hp ^ hw) of the K block (or the block's only group).
-    const int gshift = (pr.g == 128) ? 1 : 0;
+    // alpha for one tile: the (up to) two groups of the K block x Q planes, fetched one tile ahead
+    // with loads whose address is "per-lane column pointer + warp-uniform offset".  Columns past
+    // N are clamped to N-1 (their results are never stored), so the loads need no predicate.
+    const int two_groups = (pr.g == 128) ? 1 : 0;
     const int gdiv = pr.g / 128;  // 128-feature units per group
-    const size_t a_plane = (size_t)N;
     auto load_alpha = [&](int kb, int sub, __half(&dst)[2][Q]) {
-        const int n = (sub_begin + sub) * CW + col;
-        const bool ok = n < N && !(P.ablate & 1);
-        const int g0 = gshift ? (2 * kb + hw) : (2 * kb) / gdiv;
-        const int g1 = gshift ? (2 * kb + (hw ^ 1)) : g0;
-        const __half *p0 = pr.alpha + (size_t)g0 * Q * a_plane + n;
-        const __half *p1 = pr.alpha + (size_t)g1 * Q * a_plane + n;
+        const int n = min((sub_begin + sub) * CW + col, N - 1);
+        const int g0 = two_groups ? 2 * kb : (2 * kb) / gdiv;
+        const __half *p0 = pr.alpha + n;
+        const size_t off0 = (size_t)g0 * Q * (size_t)N;
+        const size_t off1 = off0 + (two_groups ? (size_t)Q * (size_t)N : 0);
 #pragma unroll
         for (int b = 0; b < Q; ++b) {
-            dst[0][b] = ok ? __ldg(p0 + b * a_plane) : __float2half(0.f);
-            dst[1][b] = ok ? __ldg(p1 + b * a_plane) : __float2half(0.f);
+            dst[0][b] = __ldg(p0 + off0 + (size_t)b * N);
+            dst[1][b] = __ldg(p0 + off1 + (size_t)b * N);
         }
     };
     __half a_next[2][Q];
-    if (kb_begin < kb_end) load_alpha(kb_begin, 0, a_next);  // constants: legal before the dependency wait
+    if (kb_begin < kb_end && !(P.ablate & 1)) load_alpha(kb_begin, 0, a_next);  // constants: legal before the dependency wait
+    else {
+#pragma unroll
+        for (int b = 0; b < Q; ++b) a_next[0][b] = a_next[1][b] = __float2half(0.f);
+    }
 
     pdl_wait();  // activations, bias, y and the scratch buffer may be written by the previous kernel
 
@@ -378,7 +381,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                 {
                     const bool more_sub = (sub + 1 < nsub);
                     const int kb_n = more_sub ? kb : kb + 1;
-                    if (kb_n < kb_end) load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
+                    if (kb_n < kb_end && !(P.ablate & 1)) load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
                 }
                 mbar_wait(full0 + 8 * st, phase, P.status);
                 const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
@@ -410,7 +413,10 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                         }
                     }
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) a_sub += __half2float(a_cur[hp][b]) * (part[b] + part2[b]);
+                    for (int b = 0; b < Q; ++b) {
+                        const __half a = (hp ^ hw) ? a_cur[1][b] : a_cur[0][b];  // slot hp holds group hp ^ hw
+                        a_sub += __half2float(a) * (part[b] + part2[b]);
+                    }
                 }
                 acc[sub] += a_sub;
                 __syncwarp();
