@@ -1,0 +1,249 @@
+"""Batch-1 decode harness for LLaMA-architecture models whose linear layers are BCQ `LutLinear`s.
+
+The reference wires its kernels into a decode benchmark for OPT only (`benchmark()`,
+model/opt.py:366-423: 100 warm-up single-token forwards, then per-token forward + device sync,
+median seconds per token).  This module is the same measurement for the LLaMA family
+(model/llama.py:93-98 names the linears that get replaced): every q/k/v/o/gate/up/down
+projection is a `LutLinear` (mode A), attention, RMSNorm, RoPE and `lm_head` stay in fp16
+torch, as BASELINE.json's decoder configuration states.  Weights are synthetic (no checkpoints
+offline): embeddings / lm_head N(0, 0.02), BCQ planes uniform +-1, alpha = 2**-k.
+
+One decode step issues, per block: RMSNorm, ONE grouped launch for q/k/v, RoPE + cache write,
+attention over a static KV cache, o_proj, RMSNorm, ONE grouped launch for gate/up, SiLU*up,
+down_proj; all LUT launches use programmatic dependent launch.  The whole step (including the
+greedy argmax and the position increment) is captured in a CUDA graph, so a token costs one
+graph replay and no host work.
+
+    python -m shiftaddllm_b200.decoder --model llama2-7b --prompt 512 --new 128
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import statistics
+import time
+from dataclasses import dataclass
+
+import torch
+import torch.nn.functional as F
+
+from . import lutgemm
+from .quant import LutLinear
+
+
+@dataclass
+class LlamaShape:
+    hidden: int
+    layers: int
+    heads: int
+    kv_heads: int
+    ffn: int
+    vocab: int = 32000
+    rope_theta: float = 10000.0
+    eps: float = 1e-5
+
+    @property
+    def head_dim(self) -> int:
+        return self.hidden // self.heads
+
+
+SHAPES = {
+    "llama2-7b": LlamaShape(4096, 32, 32, 32, 11008),
+    "llama2-70b": LlamaShape(8192, 80, 64, 8, 28672),
+    "tiny": LlamaShape(256, 2, 4, 2, 512, vocab=1000),
+}
+
+
+def _synthetic_lut_linear(k, n, q, g, device, gen) -> LutLinear:
+    lin = LutLinear(k, n, g, q, bias=None)
+    lin.binaryWeight = torch.randint(-2 ** 31, 2 ** 31, (k // 32, q, n), dtype=torch.int32, device=device, generator=gen)
+    lin.alpha = torch.exp2(-torch.randint(2, 9, (k // g, q, n), device=device, generator=gen).float()).half()
+    lin.alpha_layout = "row"
+    return lin
+
+
+class _Block:
+    def __init__(self, shape: LlamaShape, q, g, device, gen):
+        h, kv = shape.hidden, shape.kv_heads * shape.head_dim
+        mk = lambda k, n: _synthetic_lut_linear(k, n, q, g, device, gen)
+        self.q_proj, self.k_proj, self.v_proj, self.o_proj = mk(h, h), mk(h, kv), mk(h, kv), mk(h, h)
+        self.gate_proj, self.up_proj, self.down_proj = mk(h, shape.ffn), mk(h, shape.ffn), mk(shape.ffn, h)
+        self.input_norm = (1.0 + 0.02 * torch.randn(h, device=device, generator=gen)).half()
+        self.post_norm = (1.0 + 0.02 * torch.randn(h, device=device, generator=gen)).half()
+
+    def linears(self):
+        return {"q_proj": self.q_proj, "k_proj": self.k_proj, "v_proj": self.v_proj, "o_proj": self.o_proj,
+                "gate_proj": self.gate_proj, "up_proj": self.up_proj, "down_proj": self.down_proj}
+
+
+def _group(lins, x, outs, pdl=True):
+    """One grouped LUT-GEMV launch: every layer of `lins` applied to the same activation row."""
+    probs = [dict(output=o, bWeight=l.binaryWeight, alpha=l.alpha, bias=l.bias, d_input=x, mSize=l.N, kSize=l.K,
+                  nb=l.wbit, num_groups=l.alpha.shape[0]) for l, o in zip(lins, outs)]
+    lutgemm.lutgemv_grouped(probs, pdl=pdl)
+
+
+class BcqLlamaDecoder:
+    """Greedy batch-1 decoder with a static KV cache of `max_len` positions."""
+
+    def __init__(self, shape: LlamaShape, wbits: int = 3, group_size: int = 128, max_len: int = 640, device="cuda",
+                 seed: int = 0):
+        self.shape, self.max_len = shape, max_len
+        self.device = torch.device(device)
+        gen = torch.Generator(device=self.device).manual_seed(1000003 * seed + 5)
+        self.embed = (0.02 * torch.randn(shape.vocab, shape.hidden, device=self.device, generator=gen)).half()
+        self.lm_head = (0.02 * torch.randn(shape.vocab, shape.hidden, device=self.device, generator=gen)).half()
+        self.final_norm = (1.0 + 0.02 * torch.randn(shape.hidden, device=self.device, generator=gen)).half()
+        self.blocks = [_Block(shape, wbits, group_size, self.device, gen) for _ in range(shape.layers)]
+        hd, kvh = shape.head_dim, shape.kv_heads
+        self.k_cache = torch.zeros(shape.layers, max_len, kvh, hd, dtype=torch.float16, device=self.device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        inv = 1.0 / (shape.rope_theta ** (torch.arange(0, hd, 2, device=self.device).float() / hd))
+        ang = torch.arange(max_len, device=self.device).float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()                       # [max_len, hd/2] fp32
+        self.positions = torch.arange(max_len, device=self.device)
+        # static step state (graph inputs/outputs)
+        self.token = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.logits = torch.zeros(shape.vocab, dtype=torch.float32, device=self.device)
+        h = shape.hidden
+        f16 = dict(dtype=torch.float16, device=self.device)
+        self._q, self._k, self._v = torch.empty(1, h, **f16), torch.empty(1, kvh * hd, **f16), torch.empty(1, kvh * hd, **f16)
+        self._o, self._gate, self._up = torch.empty(1, h, **f16), torch.empty(1, shape.ffn, **f16), torch.empty(1, shape.ffn, **f16)
+        self._down = torch.empty(1, h, **f16)
+        self.graph = None
+
+    # ---- one token ------------------------------------------------------------------------
+    def _rope(self, t, heads):
+        hd = self.shape.head_dim
+        cos = self.cos.index_select(0, self.pos)        # [1, hd/2]
+        sin = self.sin.index_select(0, self.pos)
+        t = t.view(heads, 2, hd // 2).float()           # rotate-half convention: (first half, second half)
+        a, b = t[:, 0, :], t[:, 1, :]
+        return torch.stack((a * cos - b * sin, b * cos + a * sin), dim=1).view(heads, hd).half()
+
+    def step(self):
+        """Consumes `self.token` at position `self.pos`; leaves logits, the greedy next token in
+        `self.token` and `self.pos + 1` in `self.pos`.  Graph-capturable (no host sync)."""
+        s = self.shape
+        hd, kvh, rep = s.head_dim, s.kv_heads, s.heads // s.kv_heads
+        x = self.embed.index_select(0, self.token)                      # [1, hidden] fp16
+        mask = (self.positions > self.pos).view(1, 1, -1)               # positions not written yet
+        for li, blk in enumerate(self.blocks):
+            hn = F.rms_norm(x, (s.hidden,), blk.input_norm, s.eps)
+            _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q, self._k, self._v))
+            qh = self._rope(self._q, s.heads)
+            kh = self._rope(self._k, kvh)
+            self.k_cache[li].index_copy_(0, self.pos, kh.view(1, kvh, hd))
+            self.v_cache[li].index_copy_(0, self.pos, self._v.view(1, kvh, hd))
+            keys = self.k_cache[li].permute(1, 2, 0)                    # [kvh, hd, T]
+            vals = self.v_cache[li].permute(1, 0, 2)                    # [kvh, T, hd]
+            scores = torch.matmul(qh.view(kvh, rep, hd), keys).float() * (1.0 / math.sqrt(hd))
+            scores = scores.masked_fill(mask, float("-inf"))
+            attn = torch.matmul(torch.softmax(scores, dim=-1).half(), vals).reshape(1, s.hidden)
+            _group((blk.o_proj,), attn, (self._o,))
+            x = x + self._o
+            hn = F.rms_norm(x, (s.hidden,), blk.post_norm, s.eps)
+            _group((blk.gate_proj, blk.up_proj), hn, (self._gate, self._up))
+            act = F.silu(self._gate) * self._up
+            _group((blk.down_proj,), act, (self._down,))
+            x = x + self._down
+        hn = F.rms_norm(x, (s.hidden,), self.final_norm, s.eps)
+        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
+        self.token.copy_(self.logits.argmax().view(1))
+        self.pos.add_(1)
+
+    def capture(self):
+        """Captures `step` in a CUDA graph (one eager warm-up step first: it sizes the workspace and
+        runs the library's one-off probes, which must not happen under capture)."""
+        stream = torch.cuda.Stream(self.device)
+        with torch.cuda.stream(stream):
+            saved = (self.token.clone(), self.pos.clone())
+            self.step()
+            torch.cuda.synchronize(self.device)
+            self.token.copy_(saved[0])
+            self.pos.copy_(saved[1])
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                self.step()
+            self.token.copy_(saved[0])
+            self.pos.copy_(saved[1])
+        torch.cuda.synchronize(self.device)
+        self.graph, self._stream = g, stream
+        return g
+
+    def reset(self, first_token: int = 0):
+        self.token.fill_(first_token)
+        self.pos.zero_()
+        self.k_cache.zero_()
+        self.v_cache.zero_()
+
+    def feed(self, token_ids):
+        """Teacher-forced pass over a prompt (fills the KV cache), one graph replay per token."""
+        run = self.graph.replay if self.graph is not None else self.step
+        for t in token_ids:
+            self.token.fill_(int(t))
+            run()
+
+    def generate(self, n):
+        run = self.graph.replay if self.graph is not None else self.step
+        out = []
+        for _ in range(n):
+            run()
+            out.append(self.token.clone())
+        return torch.cat(out)
+
+
+def benchmark(model: BcqLlamaDecoder, prompt_len: int, new_tokens: int, warmup: int = 10, seed: int = 0):
+    """tokens/s over `new_tokens` greedy decode steps after a `prompt_len`-token prompt of uniform
+    random ids (wall clock, one device sync at the end), plus the reference-style median of
+    per-token latencies measured with a sync per token (model/opt.py:405-421)."""
+    dev = model.device
+    gen = torch.Generator().manual_seed(seed)
+    prompt = torch.randint(0, model.shape.vocab, (prompt_len,), generator=gen).tolist()
+    if model.graph is None:
+        model.capture()
+    model.reset()
+    model.feed(prompt)
+    torch.cuda.synchronize(dev)
+    state = (model.token.clone(), model.pos.clone())
+    for _ in range(warmup):                      # warm-up replays on the real cache, then rewind
+        model.graph.replay()
+    model.token.copy_(state[0])
+    model.pos.copy_(state[1])
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    for _ in range(new_tokens):
+        model.graph.replay()
+    torch.cuda.synchronize(dev)
+    wall = time.perf_counter() - t0
+    model.token.copy_(state[0])
+    model.pos.copy_(state[1])
+    lat = []
+    for _ in range(new_tokens):
+        t1 = time.perf_counter()
+        model.graph.replay()
+        torch.cuda.synchronize(dev)
+        lat.append(time.perf_counter() - t1)
+    return {"tokens_per_s": new_tokens / wall, "ms_per_token": 1e3 * wall / new_tokens,
+            "median_ms_per_token_synced": 1e3 * statistics.median(lat), "prompt_len": prompt_len, "new_tokens": new_tokens}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="llama2-7b", choices=sorted(SHAPES))
+    ap.add_argument("--wbits", type=int, default=3)
+    ap.add_argument("--groupsize", type=int, default=128)
+    ap.add_argument("--prompt", type=int, default=512)
+    ap.add_argument("--new", type=int, default=128)
+    args = ap.parse_args()
+    shape = SHAPES[args.model]
+    model = BcqLlamaDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16)
+    res = benchmark(model, args.prompt, args.new)
+    res.update({"model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompt"})
+    print(json.dumps(res))
+
+
+if __name__ == "__main__":
+    main()
