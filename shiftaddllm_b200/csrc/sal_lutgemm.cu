@@ -65,14 +65,13 @@ struct TileProblem {
     __half *y;
     float *partials;     // [splits][N]
     unsigned *counters;  // [ranges]
-    int K, N;
+    int K, N, M;
     int g;               // group size along K, multiple of 128
     int kblocks;         // K / 256
     int nsub_total;      // ceil(N / CW)
     int nsub_per_range;
     int ranges, splits;
     int cta_begin;
-    int pad_;
 };
 
 struct TileParams {
@@ -189,30 +188,49 @@ struct TileCfg {
 
 // Builds the 32 tables of one K block.  Lane = chunk; a warp handles groups of
 // eight consecutive entries (entry >> 3 = hgrp).  Bank of every store = lane.
-template <int NCW>
-__device__ __forceinline__ void build_tables(const __half *__restrict__ xblk, uint32_t lut_half, int warp, int lane) {
-    const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(xblk) + lane);
-    float xf[8];
-    {
+// Builds the 32 tables of one K block.  Lane = chunk; a warp handles groups of eight consecutive
+// entries (entry >> 3 = hg).  Bank of every store = lane.  ROWS = 1: fp32 entries of activation
+// row x0.  ROWS = 2: half2 entries, low half = row x0, high half = row x1 (sums are formed in
+// fp32 and rounded once).
+template <int NCW, int ROWS>
+__device__ __forceinline__ void build_tables(const __half *__restrict__ x0, const __half *__restrict__ x1,
+                                             uint32_t lut_half, int warp, int lane) {
+    float xf[ROWS][8];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(r == 0 ? x0 : x1) + lane);
         const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const float2 f = __half22float2(h[i]);
-            xf[2 * i] = f.x;
-            xf[2 * i + 1] = f.y;
+            xf[r][2 * i] = f.x;
+            xf[r][2 * i + 1] = f.y;
         }
     }
-    float low[8];
+    float low[ROWS][8];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
-        low[i] = ((i & 1) ? xf[0] : -xf[0]) + ((i & 2) ? xf[1] : -xf[1]) + ((i & 4) ? xf[2] : -xf[2]);
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            low[r][i] = ((i & 1) ? xf[r][0] : -xf[r][0]) + ((i & 2) ? xf[r][1] : -xf[r][1]) + ((i & 4) ? xf[r][2] : -xf[r][2]);
     const uint32_t dst = lut_half + 4u * lane;
 #pragma unroll 1
     for (int hg = warp; hg < 32; hg += NCW) {
-        const float hi = ((hg & 1) ? xf[3] : -xf[3]) + ((hg & 2) ? xf[4] : -xf[4]) + ((hg & 4) ? xf[5] : -xf[5]) +
-                         ((hg & 8) ? xf[6] : -xf[6]) + ((hg & 16) ? xf[7] : -xf[7]);
+        float hi[ROWS];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sts_f32(dst + (uint32_t)(hg * 8 + i) * LUT_ROW_BYTES, hi + low[i]);
+        for (int r = 0; r < ROWS; ++r)
+            hi[r] = ((hg & 1) ? xf[r][3] : -xf[r][3]) + ((hg & 2) ? xf[r][4] : -xf[r][4]) + ((hg & 4) ? xf[r][5] : -xf[r][5]) +
+                    ((hg & 8) ? xf[r][6] : -xf[r][6]) + ((hg & 16) ? xf[r][7] : -xf[r][7]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t a = dst + (uint32_t)(hg * 8 + i) * LUT_ROW_BYTES;
+            if (ROWS == 1) {
+                sts_f32(a, hi[0] + low[0][i]);
+            } else {
+                const __half2 e = __floats2half2_rn(hi[0] + low[0][i], hi[ROWS - 1] + low[ROWS - 1][i]);
+                sts_f32(a, __uint_as_float(*reinterpret_cast<const uint32_t *>(&e)));
+            }
+        }
     }
 }
 
@@ -223,7 +241,9 @@ __device__ __forceinline__ void build_tables(const __half *__restrict__ xblk, ui
 // the status word instead of computing if it does not hold.
 constexpr uint32_t SMEM_DYNAMIC_BASE = 1024;
 
-template <int Q, int NCW, bool ABS>
+// ROWS = 1: the M = 1 kernel.  ROWS = 2: small-batch variant, blockIdx.y = pair of activation
+// rows; the same weight tile serves both rows through half2 table entries.
+template <int Q, int NCW, bool ABS, int ROWS>
 __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     lutgemv_tiled_kernel(const __grid_constant__ TileParams P) {
     using C = TileCfg<Q, NCW>;
@@ -248,7 +268,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         return;
     }
 
-    // which problem / column range / K split is this CTA
+    // which problem / column range / K split / activation rows is this CTA
     int pi = 0;
 #pragma unroll 1
     for (int i = 1; i < P.count; ++i)
@@ -258,6 +278,8 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     const int range = local % pr.ranges;
     const int split = local / pr.ranges;
     const int N = pr.N;
+    const int row0 = (int)blockIdx.y * ROWS;
+    const int rows_here = min(ROWS, pr.M - row0);
     const int sub_begin = range * pr.nsub_per_range;
     const int nsub = min(pr.nsub_per_range, pr.nsub_total - sub_begin);
     const int kb_begin = (int)(((long long)split * pr.kblocks) / pr.splits);
@@ -330,9 +352,11 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             cpack[hp][j] = pk;
         }
 
-    float acc[MAX_SUB];
+    float acc[ROWS][MAX_SUB];
 #pragma unroll
-    for (int i = 0; i < MAX_SUB; ++i) acc[i] = 0.f;
+    for (int r = 0; r < ROWS; ++r)
+#pragma unroll
+        for (int i = 0; i < MAX_SUB; ++i) acc[r][i] = 0.f;
 
     // alpha for one tile: the (up to) two groups of the K block x Q planes, fetched one tile ahead
     // with loads whose address is "per-lane column pointer + warp-uniform offset".  Columns past
@@ -360,71 +384,95 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
 
     pdl_wait();  // activations, bias, y and the scratch buffer may be written by the previous kernel
 
+    const __half *xrow0 = pr.x + (size_t)row0 * pr.K;
+    const __half *xrow1 = pr.x + (size_t)(row0 + (rows_here > 1 ? 1 : 0)) * pr.K;  // odd M: the last pair repeats its row
     int st = 0;
     uint32_t phase = 0;
     // One K block: build its tables into half `PAR` of the table rows, then walk the column tiles.
     auto process_block = [&](int kb, auto par_tag) {
         constexpr int PAR = decltype(par_tag)::value;
-        if (!(P.ablate & 2)) build_tables<NCW>(pr.x + (size_t)kb * KB_FEATS, lut_s + PAR * 128, warp, lane);
+        if (!(P.ablate & 2))
+            build_tables<NCW, ROWS>(xrow0 + (size_t)kb * KB_FEATS, xrow1 + (size_t)kb * KB_FEATS, lut_s + PAR * 128, warp, lane);
         consumer_barrier(NCW * 32);
         // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
         // unrolling it over the column tiles overflows the instruction cache.  acc[] is then
         // indexed dynamically and lives in (L1-resident) local memory: two accesses per tile.
 #pragma unroll 1
         for (int sub = 0; sub < nsub; ++sub) {
+            __half a_cur[2][Q];
+#pragma unroll
+            for (int hp = 0; hp < 2; ++hp)
+#pragma unroll
+                for (int b = 0; b < Q; ++b) a_cur[hp][b] = a_next[hp][b];
             {
-                __half a_cur[2][Q];
+                const bool more_sub = (sub + 1 < nsub);
+                const int kb_n = more_sub ? kb : kb + 1;
+                if (kb_n < kb_end && !(P.ablate & 1)) load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
+            }
+            mbar_wait(full0 + 8 * st, phase, P.status);
+            const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
+            float a_sub[ROWS];
 #pragma unroll
-                for (int hp = 0; hp < 2; ++hp)
+            for (int r = 0; r < ROWS; ++r) a_sub[r] = 0.f;
+            if (!(P.ablate & 4))
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) a_cur[hp][b] = a_next[hp][b];
-                {
-                    const bool more_sub = (sub + 1 < nsub);
-                    const int kb_n = more_sub ? kb : kb + 1;
-                    if (kb_n < kb_end && !(P.ablate & 1)) load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
-                }
-                mbar_wait(full0 + 8 * st, phase, P.status);
-                const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
-                float a_sub = 0.f;
-                if (!(P.ablate & 4))
+            for (int hp = 0; hp < 2; ++hp) {
+                float part[ROWS][Q], part2[ROWS][Q];
 #pragma unroll
-                for (int hp = 0; hp < 2; ++hp) {
-                    float part[Q], part2[Q];
+                for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) part[b] = part2[b] = 0.f;
+                    for (int b = 0; b < Q; ++b) part[r][b] = part2[r][b] = 0.f;
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t wr = wrow[hp][j] + soff;
+                for (int j = 0; j < 4; ++j) {
+                    const uint32_t wr = wrow[hp][j] + soff;
 #pragma unroll
-                        for (int b = 0; b < Q; ++b) {
-                            uint32_t w;
-                            if (b == 0) w = lds_u32_imm<0>(wr);
-                            else if (b == 1) w = lds_u32_imm<1 * BOX_COLS * 4>(wr);
-                            else if (b == 2) w = lds_u32_imm<2 * BOX_COLS * 4>(wr);
-                            else w = lds_u32_imm<3 * BOX_COLS * 4>(wr);
+                    for (int b = 0; b < Q; ++b) {
+                        uint32_t w;
+                        if (b == 0) w = lds_u32_imm<0>(wr);
+                        else if (b == 1) w = lds_u32_imm<1 * BOX_COLS * 4>(wr);
+                        else if (b == 2) w = lds_u32_imm<2 * BOX_COLS * 4>(wr);
+                        else w = lds_u32_imm<3 * BOX_COLS * 4>(wr);
+                        uint32_t e[4];
 #pragma unroll
-                            for (int t = 0; t < 4; ++t) {
-                                const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
-                                const float e = ABS ? lds_f32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off)
-                                                    : lds_f32(off + lut_s + PAR * 128);
-                                if (t & 1) part2[b] += e;
-                                else part[b] += e;
+                        for (int t = 0; t < 4; ++t) {
+                            const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
+                            e[t] = ABS ? lds_u32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off) : lds_u32_imm<0>(off + lut_s + PAR * 128);
+                        }
+                        if (ROWS == 1) {
+                            part[0][b] += __uint_as_float(e[0]);
+                            part2[0][b] += __uint_as_float(e[1]);
+                            part[0][b] += __uint_as_float(e[2]);
+                            part2[0][b] += __uint_as_float(e[3]);
+                        } else {
+                            // four half2 entries are added in fp16 (they are bounded by 8 max|x| each), then
+                            // the word's sum is widened: fp32 carries everything beyond one weight word
+                            const __half2 s01 = __hadd2(*reinterpret_cast<const __half2 *>(&e[0]), *reinterpret_cast<const __half2 *>(&e[1]));
+                            const __half2 s23 = __hadd2(*reinterpret_cast<const __half2 *>(&e[2]), *reinterpret_cast<const __half2 *>(&e[3]));
+                            const float2 f = __half22float2(__hadd2(s01, s23));
+                            if (j & 1) {
+                                part2[0][b] += f.x;
+                                part2[ROWS - 1][b] += f.y;
+                            } else {
+                                part[0][b] += f.x;
+                                part[ROWS - 1][b] += f.y;
                             }
                         }
                     }
+                }
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) {
-                        const __half a = (hp ^ hw) ? a_cur[1][b] : a_cur[0][b];  // slot hp holds group hp ^ hw
-                        a_sub += __half2float(a) * (part[b] + part2[b]);
-                    }
+                for (int b = 0; b < Q; ++b) {
+                    const float a = __half2float((hp ^ hw) ? a_cur[1][b] : a_cur[0][b]);  // slot hp holds group hp ^ hw
+#pragma unroll
+                    for (int r = 0; r < ROWS; ++r) a_sub[r] += a * (part[r][b] + part2[r][b]);
                 }
-                acc[sub] += a_sub;
-                __syncwarp();
-                if (lane == 0) mbar_arrive(empty0 + 8 * st);
-                if (++st == stages) {
-                    st = 0;
-                    phase ^= 1u;
-                }
+            }
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r) acc[r][sub] += a_sub[r];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * st);
+            if (++st == stages) {
+                st = 0;
+                phase ^= 1u;
             }
         }
     };
@@ -436,27 +484,42 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     // ---------------------------------- epilogue ----------------------------------
     if (pr.splits == 1) {
 #pragma unroll
-        for (int sub = 0; sub < MAX_SUB; ++sub) {
-            const int n = (sub_begin + sub) * CW + col;
-            if (sub < nsub && n < N) {
-                float v = acc[sub];
-                if (pr.bias) v += __half2float(pr.bias[n]);
-                if (P.accumulate) v += __half2float(pr.y[n]);
-                pr.y[n] = __float2half_rn(v);
+        for (int r = 0; r < ROWS; ++r) {
+            if (r < rows_here) {
+                __half *yrow = pr.y + (size_t)(row0 + r) * N;
+#pragma unroll
+                for (int sub = 0; sub < MAX_SUB; ++sub) {
+                    const int n = (sub_begin + sub) * CW + col;
+                    if (sub < nsub && n < N) {
+                        float v = acc[r][sub];
+                        if (pr.bias) v += __half2float(pr.bias[n]);
+                        if (P.accumulate) v += __half2float(yrow[n]);
+                        yrow[n] = __float2half_rn(v);
+                    }
+                }
             }
         }
         return;
     }
+    // partial sums: [activation row][K split][N]; arrival counters: [row pair][column range]
+    const int S = pr.splits;
+    unsigned *counter = pr.counters + (size_t)blockIdx.y * pr.ranges + range;
 #pragma unroll
-    for (int sub = 0; sub < MAX_SUB; ++sub) {
-        const int n = (sub_begin + sub) * CW + col;
-        if (sub < nsub && n < N) __stcg(&pr.partials[(size_t)split * N + n], acc[sub]);
+    for (int r = 0; r < ROWS; ++r) {
+        if (r < rows_here) {
+            float *prow = pr.partials + ((size_t)(row0 + r) * S + split) * N;
+#pragma unroll
+            for (int sub = 0; sub < MAX_SUB; ++sub) {
+                const int n = (sub_begin + sub) * CW + col;
+                if (sub < nsub && n < N) __stcg(prow + n, acc[r][sub]);
+            }
+        }
     }
     __threadfence();
     consumer_barrier(NCW * 32);
     if (tid == 0) {
-        const unsigned old = atomicAdd(&pr.counters[range], 1u);
-        s_last = (old == (unsigned)(pr.splits - 1));
+        const unsigned old = atomicAdd(counter, 1u);
+        s_last = (old == (unsigned)(S - 1));
     }
     consumer_barrier(NCW * 32);
     if (s_last) {
@@ -465,36 +528,39 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         // ascending split order (fixed, hence deterministic).  Up to 4 column tiles x 16 splits
         // = 64 independent L2 loads are in flight per thread, so the whole reduction costs one
         // or two round trips instead of one per column tile.
-        const int S = pr.splits;
-        for (int sub0 = 0; sub0 < nsub; sub0 += 4) {
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            for (int s0 = 0; s0 < S; s0 += 16) {
-                float t[4][16];
+        for (int r = 0; r < rows_here; ++r) {
+            const float *pbase = pr.partials + (size_t)(row0 + r) * S * N;
+            __half *yrow = pr.y + (size_t)(row0 + r) * N;
+            for (int sub0 = 0; sub0 < nsub; sub0 += 4) {
+                float v[4] = {0.f, 0.f, 0.f, 0.f};
+                for (int s0 = 0; s0 < S; s0 += 16) {
+                    float t[4][16];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int n = (sub_begin + sub0 + u) * CW + col;
+                        const bool live = (sub0 + u < nsub) && (n < N);
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            t[u][i] = (live && s0 + i < S) ? __ldcg(pbase + (size_t)(s0 + i) * N + n) : 0.f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) v[u] += t[u][i];
+                }
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     const int n = (sub_begin + sub0 + u) * CW + col;
-                    const bool live = (sub0 + u < nsub) && (n < N);
-#pragma unroll
-                    for (int i = 0; i < 16; ++i)
-                        t[u][i] = (live && s0 + i < S) ? __ldcg(&pr.partials[(size_t)(s0 + i) * N + n]) : 0.f;
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) v[u] += t[u][i];
-            }
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                const int n = (sub_begin + sub0 + u) * CW + col;
-                if (sub0 + u < nsub && n < N) {
-                    float r = v[u];
-                    if (pr.bias) r += __half2float(pr.bias[n]);
-                    if (P.accumulate) r += __half2float(pr.y[n]);
-                    pr.y[n] = __float2half_rn(r);
+                    if (sub0 + u < nsub && n < N) {
+                        float rsum = v[u];
+                        if (pr.bias) rsum += __half2float(pr.bias[n]);
+                        if (P.accumulate) rsum += __half2float(yrow[n]);
+                        yrow[n] = __float2half_rn(rsum);
+                    }
                 }
             }
         }
-        if (tid == 0) pr.counters[range] = 0u;  // leave the scratch buffer ready for the next call
+        if (tid == 0) *counter = 0u;  // leave the scratch buffer ready for the next call
     }
 }
 
@@ -737,9 +803,9 @@ int encode_weight_map(CUtensorMap *out, const void *bw, int K, int N, int q) {
     return r == CUDA_SUCCESS ? SAL_OK : SAL_E_LAUNCH;
 }
 
-template <int Q, int NCW, bool ABS>
-cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int smem, unsigned flags, cudaStream_t stream) {
-    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS>;
+template <int Q, int NCW, bool ABS, int ROWS>
+cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int row_groups, int smem, unsigned flags, cudaStream_t stream) {
+    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS, ROWS>;
     static int configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -749,7 +815,7 @@ cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int smem, unsign
         configured[dev] = smem;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)ctas);
+    cfg.gridDim = dim3((unsigned)ctas, (unsigned)row_groups);
     cfg.blockDim = dim3(TileCfg<Q, NCW>::THREADS);
     cfg.dynamicSmemBytes = (size_t)smem;
     cfg.stream = stream;
@@ -764,18 +830,22 @@ cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int smem, unsign
 }
 
 template <int Q>
-cudaError_t launch_tiled(const TileParams &P, int ncw, int ctas, int smem, unsigned flags, bool abs_ok, cudaStream_t stream) {
+cudaError_t launch_tiled(const TileParams &P, int ncw, int ctas, int rows, int row_groups, int smem, unsigned flags,
+                         bool abs_ok, cudaStream_t stream) {
     const bool use_abs = g_abs_override >= 0 ? (g_abs_override != 0) : abs_ok;
+    if (rows == 2)
+        return use_abs ? launch_tiled_variant<Q, 8, true, 2>(P, ctas, row_groups, smem, flags, stream)
+                       : launch_tiled_variant<Q, 8, false, 2>(P, ctas, row_groups, smem, flags, stream);
     if (ncw > 8)
-        return use_abs ? launch_tiled_variant<Q, 16, true>(P, ctas, smem, flags, stream)
-                       : launch_tiled_variant<Q, 16, false>(P, ctas, smem, flags, stream);
-    return use_abs ? launch_tiled_variant<Q, 8, true>(P, ctas, smem, flags, stream)
-                   : launch_tiled_variant<Q, 8, false>(P, ctas, smem, flags, stream);
+        return use_abs ? launch_tiled_variant<Q, 16, true, 1>(P, ctas, 1, smem, flags, stream)
+                       : launch_tiled_variant<Q, 16, false, 1>(P, ctas, 1, smem, flags, stream);
+    return use_abs ? launch_tiled_variant<Q, 8, true, 1>(P, ctas, 1, smem, flags, stream)
+                   : launch_tiled_variant<Q, 8, false, 1>(P, ctas, 1, smem, flags, stream);
 }
 
 bool tiled_eligible(const void *bw, const void *alpha, const void *bias, const void *x, const void *y, int M, int K,
                     int N, int q, int num_groups) {
-    if (M != 1 || q < 1 || q > 4) return false;
+    if (M < 1 || M > SAL_MAX_M || q < 1 || q > 4) return false;
     if (K % KB_FEATS != 0 || N % 8 != 0 || N < 8) return false;
     if (num_groups <= 0 || K % num_groups != 0) return false;
     const int g = K / num_groups;
@@ -818,7 +888,12 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const int optin = dev ? dev->smem_optin : 232448;
     const int q = problems[0].q;
     int smem = 0;
-    const int ncw = g_ncw > 8 ? 16 : 8;
+    // Activation rows: M = 1 runs the fp32-table kernel; 2 <= M <= 64 runs the half2-table variant,
+    // one pair of rows per grid.y (all problems of a launch must agree on M).
+    const int M = problems[0].M;
+    const int rows = M > 1 ? 2 : 1;
+    const int row_groups = (M + rows - 1) / rows;
+    const int ncw = (rows == 1 && g_ncw > 8) ? 16 : 8;
     const int cw = ncw * 32;
     const int ctas_per_sm = ncw > 8 ? 1 : 2;
     const int stages = choose_stages(q, ncw, optin, &smem);
@@ -843,8 +918,8 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         const sal_problem &sp = problems[i];
         const double units = (double)((sp.N + cw - 1) / cw) * (sp.K / KB_FEATS);
         const int pct = g_budget_pct > 0 ? g_budget_pct : 100 * ctas_per_sm;
-        int budget = (int)(sms * (pct / 100.0) * units / units_total + 0.5);
-        if (budget < 1) budget = 1;
+        int budget = (int)(sms * (pct / 100.0) * units / units_total / row_groups + 0.5);  // row groups share the SMs
+        if (budget < 4) budget = 4;
         Plan pl = plan_problem(sp.K, sp.N, budget, have_ws, cw);
         TileProblem &tp = P.p[i];
         tp.bw = reinterpret_cast<const uint32_t *>(sp.bw);
@@ -854,6 +929,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         tp.y = reinterpret_cast<__half *>(sp.y);
         tp.K = sp.K;
         tp.N = sp.N;
+        tp.M = sp.M;
         tp.g = sp.K / sp.num_groups;
         tp.kblocks = pl.kblocks;
         tp.nsub_total = pl.nsub_total;
@@ -866,12 +942,12 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
             if (erc != SAL_OK) return erc;
         }
         if (pl.splits > 1) {
-            if (counter_off + pl.ranges > WS_MAX_COUNTERS) return SAL_E_WORKSPACE;
-            const size_t need = WS_PARTIAL_OFFSET + (n_off + (size_t)sp.N) * MAX_SPLIT * sizeof(float);
+            if (counter_off + pl.ranges * row_groups > WS_MAX_COUNTERS) return SAL_E_WORKSPACE;
+            const size_t need = WS_PARTIAL_OFFSET + (n_off + (size_t)sp.N) * (size_t)M * MAX_SPLIT * sizeof(float);
             if (!info_only && need > ws_bytes) return SAL_E_WORKSPACE;
             tp.counters = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(workspace) + WS_HEADER_BYTES) + counter_off;
-            tp.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + WS_PARTIAL_OFFSET) + n_off * MAX_SPLIT;
-            counter_off += pl.ranges;
+            tp.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + WS_PARTIAL_OFFSET) + n_off * (size_t)M * MAX_SPLIT;
+            counter_off += pl.ranges * row_groups;
         }
         n_off += (size_t)sp.N;
         cta += pl.ranges * pl.splits;
@@ -903,10 +979,10 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const bool abs_ok = dev->smem_base == (int)SMEM_DYNAMIC_BASE;
     cudaError_t e;
     switch (q) {
-        case 1: e = launch_tiled<1>(P, ncw, cta, smem, flags, abs_ok, stream); break;
-        case 2: e = launch_tiled<2>(P, ncw, cta, smem, flags, abs_ok, stream); break;
-        case 3: e = launch_tiled<3>(P, ncw, cta, smem, flags, abs_ok, stream); break;
-        default: e = launch_tiled<4>(P, ncw, cta, smem, flags, abs_ok, stream); break;
+        case 1: e = launch_tiled<1>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
+        case 2: e = launch_tiled<2>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
+        case 3: e = launch_tiled<3>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
+        default: e = launch_tiled<4>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
     }
     return cuda_ok(e) ? SAL_OK : SAL_E_LAUNCH;
 }
@@ -1107,7 +1183,7 @@ int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags, 
         int rc = validate_common(sp.bw, sp.alpha, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q);
         if (rc != SAL_OK) return rc;
         if (sp.num_groups <= 0 || sp.K % sp.num_groups != 0) return SAL_E_SHAPE;
-        if (sp.q != problems[0].q) return SAL_E_UNSUPPORTED;
+        if (sp.q != problems[0].q || sp.M != problems[0].M) return SAL_E_UNSUPPORTED;
         if (!tiled_eligible(sp.bw, sp.alpha, sp.bias, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q, sp.num_groups))
             return SAL_E_UNSUPPORTED;
     }

@@ -40,7 +40,9 @@ def test_planner_without_gpu(lib):
     assert info.smem_bytes <= 115712            # two CTAs must fit one SM
     assert lib.sal_plan_shift_scale(1, 4096, 4096, 3, 128, ctypes.byref(info)) == 0   # g = 32
     assert info.tiled == 0
-    assert lib.sal_plan_shift_scale(4, 4096, 4096, 3, 32, ctypes.byref(info)) == 0    # M > 1
+    assert lib.sal_plan_shift_scale(4, 4096, 4096, 3, 32, ctypes.byref(info)) == 0    # small batch: half2-table variant
+    assert info.tiled == 1
+    assert lib.sal_plan_shift_scale(4, 4096, 4096, 5, 32, ctypes.byref(info)) == 0    # q > 4: generic kernel
     assert info.tiled == 0
     assert lib.sal_plan_shift_scale(1, 100, 64, 3, 1, ctypes.byref(info)) == _lib.SAL_E_SHAPE
     for k, n, q in ((4096, 11008, 3), (11008, 4096, 3), (8192, 28672, 2), (28672, 8192, 2), (8192, 1024, 2), (768, 768, 3)):
