@@ -1,0 +1,45 @@
+/*
+ * sal_decode_ops.h — the element-wise / attention steps that sit between the BCQ LUT-GEMV calls
+ * of a batch-1 LLaMA-architecture decode step (same shared library as sal_lutgemm.h).
+ *
+ * The reference leaves these steps to Hugging Face's decoder layer: it only swaps the nn.Linear
+ * modules named in model/llama.py:93-98 (q/k/v/o/gate/up/down) and times the unmodified model
+ * (model/opt.py:366-423).  They are provided here fused, so that a decoded token costs a dozen
+ * launches per block instead of ~45.  All pointers are device pointers; `pos` is a DEVICE int64
+ * holding the current position, so the calls are CUDA-graph capturable with a moving position.
+ * Return values: SAL_OK or a negative SAL_E_* code (see sal_lutgemm.h).
+ */
+#ifndef SAL_DECODE_OPS_H
+#define SAL_DECODE_OPS_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* t = x (+ delta if delta != NULL); if x_out != NULL, x_out = t (the updated residual stream);
+ * out = t * rsqrt(mean(t^2) + eps) * weight.  fp16 tensors of n elements, fp32 arithmetic.
+ * x_out may alias x. */
+int sal_residual_rmsnorm_f16(const void *x, const void *delta, const void *weight, void *out, void *x_out, int n,
+                             float eps, void *stream);
+
+/* Rotary embedding (rotate-half convention) of q [heads][hd] in place and of k [kv_heads][hd] into
+ * k_cache[*pos], plus v [kv_heads][hd] into v_cache[*pos].  Caches: fp16 [max_len][kv_heads][hd].
+ * cos/sin: fp32 [max_len][hd/2]. */
+int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos, const void *sin, const int64_t *pos,
+                          void *k_cache, void *v_cache, int heads, int kv_heads, int hd, int max_len, void *stream);
+
+/* Single-query attention over cache positions 0..*pos: out [heads][hd] fp16.  Grouped-query
+ * attention when heads > kv_heads (heads % kv_heads == 0).  hd <= 256, max_len <= 16384. */
+int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
+                             int heads, int kv_heads, int hd, int max_len, float scale, void *stream);
+
+/* out = silu(gate) * up, fp16 vectors of n elements. */
+int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAL_DECODE_OPS_H */

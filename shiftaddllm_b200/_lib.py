@@ -49,6 +49,11 @@ SIGNATURES = {
     "sal_lutgemv_grouped": (_i, [ctypes.POINTER(SalProblem), _i, _u, _vp, _sz, _vp]),
     "sal_plan_shift_scale": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(SalPlanInfo)]),
     "sal_debug_set": (_i, [ctypes.c_char_p, _i]),
+    # include/sal_decode_ops.h
+    "sal_residual_rmsnorm_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _vp]),
+    "sal_rope_kv_write_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "sal_attention_decode_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp]),
+    "sal_silu_mul_f16": (_i, [_vp, _vp, _vp, _i, _vp]),
 }
 
 _lib = None

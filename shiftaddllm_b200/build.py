@@ -12,8 +12,8 @@ import sys
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 REPO_DIR = os.path.dirname(PKG_DIR)
-SRC = os.path.join(PKG_DIR, "csrc", "sal_lutgemm.cu")
-HDR = os.path.join(REPO_DIR, "include", "sal_lutgemm.h")
+SRCS = [os.path.join(PKG_DIR, "csrc", "sal_lutgemm.cu"), os.path.join(PKG_DIR, "csrc", "sal_decode_ops.cu")]
+HDRS = [os.path.join(REPO_DIR, "include", "sal_lutgemm.h"), os.path.join(REPO_DIR, "include", "sal_decode_ops.h")]
 LIB = os.path.join(PKG_DIR, "libsal_lutgemm.so")
 
 NVCC_FLAGS = [
@@ -36,13 +36,13 @@ def up_to_date() -> bool:
     if not os.path.exists(LIB):
         return False
     t = os.path.getmtime(LIB)
-    return all(os.path.getmtime(p) <= t for p in (SRC, HDR, os.path.abspath(__file__)))
+    return all(os.path.getmtime(p) <= t for p in (*SRCS, *HDRS, os.path.abspath(__file__)))
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
     if not force and up_to_date():
         return LIB
-    cmd = [find_nvcc(), *NVCC_FLAGS, "-I", os.path.join(REPO_DIR, "include"), "-o", LIB, SRC]
+    cmd = [find_nvcc(), *NVCC_FLAGS, "-I", os.path.join(REPO_DIR, "include"), "-o", LIB, *SRCS]
     if verbose:
         cmd[1:1] = ["-Xptxas", "-v"]
         print(" ".join(cmd))

@@ -1,0 +1,242 @@
+// Fused element-wise / attention steps of a batch-1 decode step (see include/sal_decode_ops.h).
+// These are latency-bound helpers (a few KB each); the point is launch count, not bandwidth.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "sal_decode_ops.h"
+#include "sal_lutgemm.h"
+
+namespace {
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum / max over up to 1024 threads through one shared array of 32 floats.
+__device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = is_max ? warp_max(v) : warp_sum(v);
+    __syncthreads();  // red may still be read from a previous call
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float r = (lane < nw) ? red[lane] : (is_max ? -INFINITY : 0.f);
+    r = is_max ? warp_max(r) : warp_sum(r);
+    return r;
+}
+
+__global__ void __launch_bounds__(1024) residual_rmsnorm_kernel(const __half *x, const __half *delta, const __half *w,
+                                                                __half *out, __half *x_out, int n, float eps) {
+    __shared__ float red[32];
+    extern __shared__ float tbuf[];  // n floats
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float t = __half2float(x[i]);
+        if (delta) t = __half2float(__float2half_rn(t + __half2float(delta[i])));  // the stream is kept in fp16
+        tbuf[i] = t;
+        ss += t * t;
+    }
+    ss = block_reduce(ss, red, false);
+    const float inv = rsqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float t = tbuf[i];
+        if (x_out) x_out[i] = __float2half_rn(t);
+        out[i] = __float2half_rn(t * inv * __half2float(w[i]));
+    }
+}
+
+// one thread per (head, pair index); q heads first, then k heads, then v copy
+__global__ void rope_kv_write_kernel(__half *q, const __half *k, const __half *v, const float *cos_t, const float *sin_t,
+                                     const int64_t *pos_p, __half *k_cache, __half *v_cache, int heads, int kv_heads,
+                                     int hd, int max_len) {
+    const int64_t pos = *pos_p;
+    if (pos < 0 || pos >= max_len) return;
+    const int half = hd / 2;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int nq = heads * half, nk = kv_heads * half, nv = kv_heads * hd;
+    if (idx < nq + nk) {
+        const bool is_q = idx < nq;
+        const int j = is_q ? idx : idx - nq;
+        const int h = j / half, i = j % half;
+        const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
+        const __half *src = is_q ? q : k;
+        const float a = __half2float(src[h * hd + i]), b = __half2float(src[h * hd + half + i]);
+        const __half ra = __float2half_rn(a * c - b * s), rb = __float2half_rn(b * c + a * s);
+        __half *dst = is_q ? q : k_cache + ((size_t)pos * kv_heads) * hd;
+        dst[h * hd + i] = ra;
+        dst[h * hd + half + i] = rb;
+    } else if (idx < nq + nk + nv) {
+        const int j = idx - nq - nk;
+        v_cache[(size_t)pos * kv_heads * hd + j] = v[j];
+    }
+}
+
+// one CTA per query head; scores for the T = pos+1 cached positions live in shared memory
+__global__ void __launch_bounds__(1024) attention_decode_kernel(const __half *q, const __half *k_cache, const __half *v_cache,
+                                                               const int64_t *pos_p, __half *out, int heads, int kv_heads,
+                                                               int hd, int max_len, float scale) {
+    extern __shared__ float smem_f[];  // hd floats (query) + max_len floats (scores) + 32*hd floats (partial outputs)
+    __shared__ float red[32];
+    float *qf = smem_f;
+    float *sc = smem_f + hd;
+    float *pbuf = sc + max_len;   // [warps][hd] partial outputs
+    const int head = blockIdx.x;
+    const int kvh = head / (heads / kv_heads);
+    int64_t pos = *pos_p;
+    if (pos >= max_len) pos = max_len - 1;
+    const int T = (int)pos + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
+    for (int i = tid; i < hd; i += blockDim.x) qf[i] = __half2float(q[head * hd + i]) * scale;
+    __syncthreads();
+    // scores: one warp per cached position, lanes over the head dimension; four positions are
+    // fetched before any of them is reduced, so that four row reads per warp are in flight
+    float lmax = -INFINITY;
+    for (int t0 = warp; t0 < T; t0 += 4 * nw) {
+        float d[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int t = t0 + u * nw;
+            d[u] = 0.f;
+            if (t < T) {
+                const __half *kr = k_cache + ((size_t)t * kv_heads + kvh) * hd;
+                for (int i = lane * 2; i < hd; i += 64) {
+                    const float2 kk = __half22float2(*reinterpret_cast<const __half2 *>(kr + i));
+                    d[u] += qf[i] * kk.x + qf[i + 1] * kk.y;
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int t = t0 + u * nw;
+            const float r = warp_sum(d[u]);
+            if (t < T) {
+                if (lane == 0) sc[t] = r;
+                lmax = fmaxf(lmax, r);
+            }
+        }
+    }
+    const float m = block_reduce(lmax, red, true);  // also publishes sc[] (barriers inside)
+    float lsum = 0.f;
+    for (int t = tid; t < T; t += blockDim.x) {
+        const float p = __expf(sc[t] - m);
+        sc[t] = p;
+        lsum += p;
+    }
+    const float denom = block_reduce(lsum, red, false);
+    __syncthreads();
+    // output: every warp takes every nw-th position (one coalesced row read each, many in flight),
+    // lanes over the head dimension; the per-warp partial outputs are then added up in shared memory
+    float2 o[4];   // hd <= 256: up to four half2 per lane
+#pragma unroll
+    for (int u = 0; u < 4; ++u) o[u] = make_float2(0.f, 0.f);
+    for (int t0 = warp; t0 < T; t0 += 4 * nw) {
+        float2 vv[4][4];
+        float p[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {          // issue the row reads of four positions first
+            const int t = t0 + k * nw;
+            p[k] = (t < T) ? sc[t] : 0.f;
+            const __half *vr = v_cache + ((size_t)(t < T ? t : 0) * kv_heads + kvh) * hd;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = lane * 2 + u * 64;
+                vv[k][u] = (i < hd) ? __half22float2(*reinterpret_cast<const __half2 *>(vr + i)) : make_float2(0.f, 0.f);
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                o[u].x += p[k] * vv[k][u].x;
+                o[u].y += p[k] * vv[k][u].y;
+            }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const int i = lane * 2 + u * 64;
+        if (i < hd) {
+            pbuf[warp * hd + i] = o[u].x;
+            pbuf[warp * hd + i + 1] = o[u].y;
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < hd; i += blockDim.x) {
+        float r = 0.f;
+        for (int w = 0; w < nw; ++w) r += pbuf[w * hd + i];
+        out[head * hd + i] = __float2half_rn(r / denom);
+    }
+}
+
+__global__ void silu_mul_kernel(const __half *gate, const __half *up, __half *out, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) {
+        const float g = __half2float(gate[i]);
+        out[i] = __float2half_rn(__half2float(__float2half_rn(g / (1.f + __expf(-g)))) * __half2float(up[i]));
+    }
+}
+
+inline int launch_status() { return cudaGetLastError() == cudaSuccess ? SAL_OK : SAL_E_LAUNCH; }
+
+}  // namespace
+
+extern "C" {
+
+int sal_residual_rmsnorm_f16(const void *x, const void *delta, const void *weight, void *out, void *x_out, int n, float eps,
+                             void *stream) {
+    if (!x || !weight || !out) return SAL_E_NULL;
+    if (n < 1 || n > 32768) return SAL_E_SHAPE;
+    const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
+    residual_rmsnorm_kernel<<<1, threads, (size_t)n * sizeof(float), reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half *>(x), reinterpret_cast<const __half *>(delta), reinterpret_cast<const __half *>(weight),
+        reinterpret_cast<__half *>(out), reinterpret_cast<__half *>(x_out), n, eps);
+    return launch_status();
+}
+
+int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos, const void *sin, const int64_t *pos,
+                          void *k_cache, void *v_cache, int heads, int kv_heads, int hd, int max_len, void *stream) {
+    if (!q || !k || !v || !cos || !sin || !pos || !k_cache || !v_cache) return SAL_E_NULL;
+    if (heads < 1 || kv_heads < 1 || hd < 2 || (hd & 1) || max_len < 1) return SAL_E_SHAPE;
+    const int total = heads * (hd / 2) + kv_heads * (hd / 2) + kv_heads * hd;
+    rope_kv_write_kernel<<<(total + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<__half *>(q), reinterpret_cast<const __half *>(k), reinterpret_cast<const __half *>(v),
+        reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin), pos, reinterpret_cast<__half *>(k_cache),
+        reinterpret_cast<__half *>(v_cache), heads, kv_heads, hd, max_len);
+    return launch_status();
+}
+
+int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int heads,
+                             int kv_heads, int hd, int max_len, float scale, void *stream) {
+    if (!q || !k_cache || !v_cache || !pos || !out) return SAL_E_NULL;
+    if (heads < 1 || kv_heads < 1 || heads % kv_heads || hd < 2 || hd > 256 || (hd & 1) || max_len < 1 || max_len > 16384)
+        return SAL_E_SHAPE;
+    const size_t smem = (size_t)(hd + max_len + 32 * hd) * sizeof(float);
+    if (smem > 48 * 1024) {
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) != cudaSuccess)
+                return SAL_E_LAUNCH;
+            configured = true;
+        }
+    }
+    attention_decode_kernel<<<heads, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k_cache), reinterpret_cast<const __half *>(v_cache),
+        pos, reinterpret_cast<__half *>(out), heads, kv_heads, hd, max_len, scale);
+    return launch_status();
+}
+
+int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream) {
+    if (!gate || !up || !out) return SAL_E_NULL;
+    if (n < 1) return SAL_E_SHAPE;
+    silu_mul_kernel<<<(n + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __half *>(gate), reinterpret_cast<const __half *>(up), reinterpret_cast<__half *>(out), n);
+    return launch_status();
+}
+
+}  // extern "C"

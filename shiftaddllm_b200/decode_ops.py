@@ -1,0 +1,40 @@
+"""Python face of include/sal_decode_ops.h: the fused steps between the LUT-GEMV calls of a
+batch-1 decode step.  Tensors must be contiguous CUDA tensors; launches go to torch's current
+stream and are CUDA-graph capturable (the position is read from a device tensor)."""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def residual_rmsnorm(x, delta, weight, out, x_out, eps: float):
+    """t = x (+ delta); x_out = t (if given, may be x itself); out = rmsnorm(t) * weight."""
+    lib = _lib.load()
+    _lib.check(lib.sal_residual_rmsnorm_f16(x.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
+                                            out.data_ptr(), None if x_out is None else x_out.data_ptr(), x.numel(),
+                                            float(eps), _stream(x)), "sal_residual_rmsnorm_f16")
+
+
+def rope_kv_write(q, k, v, cos, sin, pos, k_cache, v_cache, heads, kv_heads, hd):
+    lib = _lib.load()
+    _lib.check(lib.sal_rope_kv_write_f16(q.data_ptr(), k.data_ptr(), v.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                         pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), heads, kv_heads, hd,
+                                         k_cache.shape[0], _stream(q)), "sal_rope_kv_write_f16")
+
+
+def attention_decode(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, scale: float):
+    lib = _lib.load()
+    _lib.check(lib.sal_attention_decode_f16(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(),
+                                            out.data_ptr(), heads, kv_heads, hd, k_cache.shape[0], float(scale),
+                                            _stream(q)), "sal_attention_decode_f16")
+
+
+def silu_mul(gate, up, out):
+    lib = _lib.load()
+    _lib.check(lib.sal_silu_mul_f16(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _stream(gate)),
+               "sal_silu_mul_f16")

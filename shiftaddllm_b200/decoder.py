@@ -28,7 +28,7 @@ from dataclasses import dataclass
 import torch
 import torch.nn.functional as F
 
-from . import lutgemm
+from . import decode_ops, lutgemm
 from .quant import LutLinear
 
 
@@ -88,8 +88,9 @@ class BcqLlamaDecoder:
     """Greedy batch-1 decoder with a static KV cache of `max_len` positions."""
 
     def __init__(self, shape: LlamaShape, wbits: int = 3, group_size: int = 128, max_len: int = 640, device="cuda",
-                 seed: int = 0):
+                 seed: int = 0, fused: bool = True):
         self.shape, self.max_len = shape, max_len
+        self.fused = fused   # fused CUDA helpers between the GEMVs (False: plain torch ops)
         self.device = torch.device(device)
         gen = torch.Generator(device=self.device).manual_seed(1000003 * seed + 5)
         self.embed = (0.02 * torch.randn(shape.vocab, shape.hidden, device=self.device, generator=gen)).half()
@@ -112,6 +113,8 @@ class BcqLlamaDecoder:
         self._q, self._k, self._v = torch.empty(1, h, **f16), torch.empty(1, kvh * hd, **f16), torch.empty(1, kvh * hd, **f16)
         self._o, self._gate, self._up = torch.empty(1, h, **f16), torch.empty(1, shape.ffn, **f16), torch.empty(1, shape.ffn, **f16)
         self._down = torch.empty(1, h, **f16)
+        self._x, self._hn = torch.empty(1, h, **f16), torch.empty(1, h, **f16)
+        self._attn, self._act = torch.empty(1, h, **f16), torch.empty(1, shape.ffn, **f16)
         self.graph = None
 
     # ---- one token ------------------------------------------------------------------------
@@ -126,6 +129,8 @@ class BcqLlamaDecoder:
     def step(self):
         """Consumes `self.token` at position `self.pos`; leaves logits, the greedy next token in
         `self.token` and `self.pos + 1` in `self.pos`.  Graph-capturable (no host sync)."""
+        if self.fused:
+            return self._step_fused()
         s = self.shape
         hd, kvh, rep = s.head_dim, s.kv_heads, s.heads // s.kv_heads
         x = self.embed.index_select(0, self.token)                      # [1, hidden] fp16
@@ -150,6 +155,32 @@ class BcqLlamaDecoder:
             _group((blk.down_proj,), act, (self._down,))
             x = x + self._down
         hn = F.rms_norm(x, (s.hidden,), self.final_norm, s.eps)
+        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
+        self.token.copy_(self.logits.argmax().view(1))
+        self.pos.add_(1)
+
+    def _step_fused(self):
+        """Same step with the fused helpers of include/sal_decode_ops.h: per block 4 LUT-GEMV
+        launches + 5 helper launches (residual+RMSNorm x2, RoPE+cache write, attention, SiLU*up)."""
+        s = self.shape
+        hd, kvh = s.head_dim, s.kv_heads
+        scale = 1.0 / math.sqrt(hd)
+        x, hn = self._x, self._hn
+        torch.index_select(self.embed, 0, self.token, out=x)
+        delta = None
+        for li, blk in enumerate(self.blocks):
+            decode_ops.residual_rmsnorm(x, delta, blk.input_norm, hn, x, s.eps)
+            _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q, self._k, self._v))
+            decode_ops.rope_kv_write(self._q, self._k, self._v, self.cos, self.sin, self.pos, self.k_cache[li],
+                                     self.v_cache[li], s.heads, kvh, hd)
+            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale)
+            _group((blk.o_proj,), self._attn, (self._o,))
+            decode_ops.residual_rmsnorm(x, self._o, blk.post_norm, hn, x, s.eps)
+            _group((blk.gate_proj, blk.up_proj), hn, (self._gate, self._up))
+            decode_ops.silu_mul(self._gate, self._up, self._act)
+            _group((blk.down_proj,), self._act, (self._down,))
+            delta = self._down
+        decode_ops.residual_rmsnorm(x, delta, self.final_norm, hn, x, s.eps)
         self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
         self.token.copy_(self.logits.argmax().view(1))
         self.pos.add_(1)
@@ -237,11 +268,12 @@ def main():
     ap.add_argument("--groupsize", type=int, default=128)
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new", type=int, default=128)
+    ap.add_argument("--no-fused", action="store_true", help="plain torch ops between the GEMVs")
     args = ap.parse_args()
     shape = SHAPES[args.model]
-    model = BcqLlamaDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16)
+    model = BcqLlamaDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16, fused=not args.no_fused)
     res = benchmark(model, args.prompt, args.new)
-    res.update({"model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompt"})
+    res.update({"fused_helpers": not args.no_fused, "model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompt"})
     print(json.dumps(res))
 
 

@@ -56,8 +56,61 @@ def reference_logits(model, tokens):
     return (hn @ model.lm_head.float().t()).view(-1)
 
 
-def test_tiny_decoder_matches_fp32_reference():
-    model = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, group_size=128, max_len=32, seed=1)
+def test_fused_helpers_match_torch():
+    from shiftaddllm_b200 import decode_ops
+
+    g = torch.Generator(device="cuda").manual_seed(0)
+    n = 4096
+    x = torch.randn(1, n, device="cuda", generator=g).half()
+    d = torch.randn(1, n, device="cuda", generator=g).half()
+    w = (1 + 0.1 * torch.randn(n, device="cuda", generator=g)).half()
+    out, xo = torch.empty_like(x), torch.empty_like(x)
+    decode_ops.residual_rmsnorm(x, d, w, out, xo, 1e-5)
+    t = (x + d)
+    ref = (t.float() * torch.rsqrt(t.float().pow(2).mean() + 1e-5) * w.float())
+    assert torch.equal(xo, t) and float((out.float() - ref).abs().max()) < 4e-3
+    decode_ops.residual_rmsnorm(x, None, w, out, None, 1e-5)
+    ref = x.float() * torch.rsqrt(x.float().pow(2).mean() + 1e-5) * w.float()
+    assert float((out.float() - ref).abs().max()) < 4e-3
+    gate, up = torch.randn(11008, device="cuda", generator=g).half(), torch.randn(11008, device="cuda", generator=g).half()
+    act = torch.empty_like(gate)
+    decode_ops.silu_mul(gate, up, act)
+    assert float((act.float() - (F.silu(gate) * up).float()).abs().max()) < 4e-3
+    # rope + cache write + attention, grouped-query (8 heads on 2 kv heads)
+    heads, kvh, hd, max_len, pos_v = 8, 2, 64, 40, 17
+    q = torch.randn(heads * hd, device="cuda", generator=g).half()
+    k = torch.randn(kvh * hd, device="cuda", generator=g).half()
+    v = torch.randn(kvh * hd, device="cuda", generator=g).half()
+    kc = torch.randn(max_len, kvh, hd, device="cuda", generator=g).half()
+    vc = torch.randn(max_len, kvh, hd, device="cuda", generator=g).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+    ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([pos_v], device="cuda")
+
+    def rope(t, nh):
+        t = t.view(nh, 2, hd // 2).float()
+        a, b = t[:, 0], t[:, 1]
+        return torch.stack((a * cos[pos_v] - b * sin[pos_v], b * cos[pos_v] + a * sin[pos_v]), 1).view(nh, hd).half()
+
+    q_ref, k_ref = rope(q, heads), rope(k, kvh)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    kc_ref[pos_v], vc_ref[pos_v] = k_ref, v.view(kvh, hd)
+    decode_ops.rope_kv_write(q, k, v, cos, sin, pos, kc, vc, heads, kvh, hd)
+    assert float((q.view(heads, hd).float() - q_ref.float()).abs().max()) < 2e-3
+    assert float((kc.float() - kc_ref.float()).abs().max()) < 2e-3 and torch.equal(vc, vc_ref)
+    out = torch.empty(heads * hd, dtype=torch.float16, device="cuda")
+    decode_ops.attention_decode(q, kc, vc, pos, out, heads, kvh, hd, 1.0 / math.sqrt(hd))
+    kk = kc[: pos_v + 1].float().repeat_interleave(heads // kvh, dim=1)      # [T, heads, hd]
+    vv = vc[: pos_v + 1].float().repeat_interleave(heads // kvh, dim=1)
+    sc = torch.einsum("hd,thd->ht", q.view(heads, hd).float(), kk) / math.sqrt(hd)
+    ref = torch.einsum("ht,thd->hd", torch.softmax(sc, -1), vv).reshape(-1)
+    assert float((out.float() - ref).abs().max()) < 4e-3
+
+
+@pytest.mark.parametrize("fused", [False, True])
+def test_tiny_decoder_matches_fp32_reference(fused):
+    model = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, group_size=128, max_len=32, seed=1, fused=fused)
     tokens = [5, 17, 999, 3, 42, 7]
     model.reset()
     for i, t in enumerate(tokens):
