@@ -9,6 +9,13 @@
 
 namespace {
 
+// Programmatic dependent launch: let the next kernel of the stream start (it may prefetch its
+// constant operands), then wait until the previous kernel's results are visible.
+__device__ __forceinline__ void pdl_prologue() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -36,6 +43,7 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_kernel(const __half *x,
                                                                 __half *out, __half *x_out, int n, float eps) {
     __shared__ float red[32];
     extern __shared__ float tbuf[];  // n floats
+    pdl_prologue();
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float t = __half2float(x[i]);
@@ -56,6 +64,7 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_kernel(const __half *x,
 __global__ void rope_kv_write_kernel(__half *q, const __half *k, const __half *v, const float *cos_t, const float *sin_t,
                                      const int64_t *pos_p, __half *k_cache, __half *v_cache, int heads, int kv_heads,
                                      int hd, int max_len) {
+    pdl_prologue();
     const int64_t pos = *pos_p;
     if (pos < 0 || pos >= max_len) return;
     const int half = hd / 2;
@@ -84,6 +93,7 @@ __global__ void __launch_bounds__(1024) attention_decode_kernel(const __half *q,
                                                                int hd, int max_len, float scale) {
     extern __shared__ float smem_f[];  // hd floats (query) + max_len floats (scores) + 32*hd floats (partial outputs)
     __shared__ float red[32];
+    pdl_prologue();
     float *qf = smem_f;
     float *sc = smem_f + hd;
     float *pbuf = sc + max_len;   // [warps][hd] partial outputs
@@ -175,6 +185,7 @@ __global__ void __launch_bounds__(1024) attention_decode_kernel(const __half *q,
 }
 
 __global__ void silu_mul_kernel(const __half *gate, const __half *up, __half *out, int n) {
+    pdl_prologue();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) {
         const float g = __half2float(gate[i]);
@@ -182,7 +193,21 @@ __global__ void silu_mul_kernel(const __half *gate, const __half *up, __half *ou
     }
 }
 
-inline int launch_status() { return cudaGetLastError() == cudaSuccess ? SAL_OK : SAL_E_LAUNCH; }
+// All helpers are launched with the programmatic-stream-serialization attribute (see pdl_prologue).
+template <typename... KArgs, typename... Args>
+int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, void *stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? SAL_OK : SAL_E_LAUNCH;
+}
 
 }  // namespace
 
@@ -193,10 +218,10 @@ int sal_residual_rmsnorm_f16(const void *x, const void *delta, const void *weigh
     if (!x || !weight || !out) return SAL_E_NULL;
     if (n < 1 || n > 32768) return SAL_E_SHAPE;
     const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
-    residual_rmsnorm_kernel<<<1, threads, (size_t)n * sizeof(float), reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __half *>(x), reinterpret_cast<const __half *>(delta), reinterpret_cast<const __half *>(weight),
-        reinterpret_cast<__half *>(out), reinterpret_cast<__half *>(x_out), n, eps);
-    return launch_status();
+    return launch_pdl(residual_rmsnorm_kernel, dim3(1), dim3(threads), (size_t)n * sizeof(float), stream,
+                      reinterpret_cast<const __half *>(x), reinterpret_cast<const __half *>(delta),
+                      reinterpret_cast<const __half *>(weight), reinterpret_cast<__half *>(out),
+                      reinterpret_cast<__half *>(x_out), n, eps);
 }
 
 int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos, const void *sin, const int64_t *pos,
@@ -204,11 +229,10 @@ int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos
     if (!q || !k || !v || !cos || !sin || !pos || !k_cache || !v_cache) return SAL_E_NULL;
     if (heads < 1 || kv_heads < 1 || hd < 2 || (hd & 1) || max_len < 1) return SAL_E_SHAPE;
     const int total = heads * (hd / 2) + kv_heads * (hd / 2) + kv_heads * hd;
-    rope_kv_write_kernel<<<(total + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<__half *>(q), reinterpret_cast<const __half *>(k), reinterpret_cast<const __half *>(v),
-        reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin), pos, reinterpret_cast<__half *>(k_cache),
-        reinterpret_cast<__half *>(v_cache), heads, kv_heads, hd, max_len);
-    return launch_status();
+    return launch_pdl(rope_kv_write_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, reinterpret_cast<__half *>(q),
+                      reinterpret_cast<const __half *>(k), reinterpret_cast<const __half *>(v),
+                      reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin), pos,
+                      reinterpret_cast<__half *>(k_cache), reinterpret_cast<__half *>(v_cache), heads, kv_heads, hd, max_len);
 }
 
 int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int heads,
@@ -225,18 +249,16 @@ int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_c
             configured = true;
         }
     }
-    attention_decode_kernel<<<heads, 1024, smem, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k_cache), reinterpret_cast<const __half *>(v_cache),
-        pos, reinterpret_cast<__half *>(out), heads, kv_heads, hd, max_len, scale);
-    return launch_status();
+    return launch_pdl(attention_decode_kernel, dim3(heads), dim3(1024), smem, stream, reinterpret_cast<const __half *>(q),
+                      reinterpret_cast<const __half *>(k_cache), reinterpret_cast<const __half *>(v_cache), pos,
+                      reinterpret_cast<__half *>(out), heads, kv_heads, hd, max_len, scale);
 }
 
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream) {
     if (!gate || !up || !out) return SAL_E_NULL;
     if (n < 1) return SAL_E_SHAPE;
-    silu_mul_kernel<<<(n + 255) / 256, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-        reinterpret_cast<const __half *>(gate), reinterpret_cast<const __half *>(up), reinterpret_cast<__half *>(out), n);
-    return launch_status();
+    return launch_pdl(silu_mul_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, reinterpret_cast<const __half *>(gate),
+                      reinterpret_cast<const __half *>(up), reinterpret_cast<__half *>(out), n);
 }
 
 }  // extern "C"
