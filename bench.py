@@ -36,13 +36,28 @@ import torch
 REPO = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, REPO)
 
-LAYERS = 32
-Q, G = 3, 128
-GROUPS = ((("q_proj", 4096, 4096), ("k_proj", 4096, 4096), ("v_proj", 4096, 4096)),
-          (("o_proj", 4096, 4096),),
-          (("gate_proj", 4096, 11008), ("up_proj", 4096, 11008)),
-          (("down_proj", 11008, 4096),))
+WORKLOADS = {
+    # name: (decoder blocks, wbits, per-block launch groups of (name, K, N))
+    "llama2-7b": (32, 3, ((("q_proj", 4096, 4096), ("k_proj", 4096, 4096), ("v_proj", 4096, 4096)),
+                          (("o_proj", 4096, 4096),),
+                          (("gate_proj", 4096, 11008), ("up_proj", 4096, 11008)),
+                          (("down_proj", 11008, 4096),))),
+    # the configuration the column-parallel scheme is meant for (2-bit, GQA); not the default
+    "llama2-70b": (80, 2, ((("q_proj", 8192, 8192), ("k_proj", 8192, 1024), ("v_proj", 8192, 1024)),
+                           (("o_proj", 8192, 8192),),
+                           (("gate_proj", 8192, 28672), ("up_proj", 8192, 28672)),
+                           (("down_proj", 28672, 8192),))),
+}
+G = 128
+LAYERS, Q, GROUPS = WORKLOADS["llama2-7b"]
 METRIC = "BCQ LUT-GEMV HBM GB/s, LLaMA-2-7B 3-bit g128 decode linear set, M=1"
+
+
+def select_workload(name):
+    global LAYERS, Q, GROUPS, METRIC
+    LAYERS, Q, GROUPS = WORKLOADS[name]
+    if name != "llama2-7b":
+        METRIC = f"BCQ LUT-GEMV HBM GB/s, {name} {Q}-bit g128 decode linear set, M=1"
 
 
 def algorithmic_bytes(k, n, q=Q, g=G, m=1):
@@ -255,19 +270,20 @@ def run_ours(args, rank, world, device):
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16 in, fp32 accumulate",
         "data": "synthetic", "impl": "ours",
-        "config": {"workload": "LLaMA-2-7B decode linear set (32 blocks x 7 linears), M=1, BCQ 3-bit g128",
+        "config": {"workload": f"{args.workload} decode linear set ({LAYERS} blocks x 7 linears), M=1, BCQ {Q}-bit g128",
                    "launches_per_step": n_launch,
                    "launch_structure": ("one grouped launch per decoder block (7 independent products); PDL chained; "
                                         + ("CUDA graph" if graphed else "eager")),
-                   "l2": "inputs larger than L2 (2.7 GB of weights per step), no flush",
+                   "l2": f"inputs larger than L2 ({total / 1e9:.1f} GB of weights per step), no flush",
                    "parallelism": f"column-parallel x{world} + NCCL all-gather" if world > 1 else "single GPU"},
         "tokens_per_s_linears_only": round(1e3 / ms_per_step, 1),
         "gemv_per_s": round(LAYERS * 7 * 1e3 / ms_per_step, 1),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                      "frac": round(achieved / peak, 4), "frac_of_nominal_8000": round(achieved / 8000.0, 4),
                      "peak_source": f"{which} copy bandwidth (MEASURED_PEAKS.json)" if which == "measured" else "fallback 6650",
-                     "kernel": "lutgemv_tiled_kernel<3,8>", "avg_launch_us": round(per_launch_us, 3),
-                     "algorithmic_bytes_per_launch": total // world // n_launch, "traffic": read_traffic()},
+                     "kernel": f"lutgemv_tiled_kernel<{Q},8>", "avg_launch_us": round(per_launch_us, 3),
+                     "algorithmic_bytes_per_launch": total // world // n_launch,
+                     "traffic": read_traffic() if (args.workload == "llama2-7b" and world == 1) else None},
         "e2e": {"value": round(total / e2e_s / 1e9, 1), "unit": "GB/s", "ms_per_step": round(e2e_s * 1e3, 3),
                 "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
                 "api": "shiftaddllm_b200.lutgemm.lutgemv_grouped (eager Python calls), pinned host buffers"},
@@ -364,7 +380,7 @@ def run_reference(args, rank, world):
     return {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3),
             "ms_per_step": round(dt * 1e3, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "fp32", "data": "synthetic", "impl": "reference",
-            "config": {"workload": "LLaMA-2-7B decode linear set, M=1, BCQ 3-bit g128", "sample": sample},
+            "config": {"workload": f"{args.workload} decode linear set, M=1, BCQ {Q}-bit g128", "sample": sample},
             "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -377,7 +393,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="llama2-7b", choices=sorted(WORKLOADS),
+                    help="linear set to run (default: the configuration the headline metric is quoted on)")
     args = ap.parse_args()
+    select_workload(args.workload)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
