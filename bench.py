@@ -150,7 +150,15 @@ def run_ours(args, rank, world, device):
     n_out = sum(n for grp in GROUPS for _, _, n in grp) * LAYERS
     x_all = torch.randn(n_in, device=device, generator=gen).half()
     y_all = torch.zeros(n_out // world, dtype=torch.float16, device=device)
-    y_full = torch.zeros(n_out, dtype=torch.float16, device=device) if world > 1 else None
+    fused = world > 1 and args.exchange == "fused"
+    peer = None
+    if fused:
+        from shiftaddllm_b200.exchange import PeerExchange
+
+        peer = PeerExchange.symmetric(n_out, nslots=4)
+        y_full = peer.buffer
+    else:
+        y_full = torch.zeros(n_out, dtype=torch.float16, device=device) if world > 1 else None
     def make_launches(per_block_groups):
         """per_block_groups: lists of product indices (0..6 within a block) sharing one launch."""
         launches = []
@@ -169,20 +177,31 @@ def run_ours(args, rank, world, device):
                     plist.append(dict(output=y, bWeight=p["bw"], alpha=p["alpha"], bias=None, d_input=x,
                                       mSize=p["N_loc"], kSize=p["K"], nb=Q, num_groups=p["K"] // G))
                 gathered = None
-                if world > 1:   # the launch's output slices are contiguous in y_all: one all-gather per launch
+                if world > 1:   # the launch's output slices are contiguous in y_all: one exchange per launch
                     lo = views[idxs[0]][2]
                     hi = views[idxs[-1]][2] + flat[idxs[-1]]["N_loc"]
-                    gathered = (y_full[yfi:yfi + (hi - lo) * world], y_all[lo:hi])
-                    yfi += (hi - lo) * world
+                    if fused:   # every product owns a [world][N_loc] block of the gather buffer
+                        offs = []
+                        for i in idxs:
+                            offs.append(yfi)
+                            yfi += flat[i]["N"]
+                        gathered = offs
+                    else:
+                        gathered = (y_full[yfi:yfi + (hi - lo) * world], y_all[lo:hi])
+                        yfi += (hi - lo) * world
                 launches.append((plist, gathered))
         return launches
 
     def make_step(launches):
         def one_step():
-            for plist, gathered in launches:
-                lutgemm.lutgemv_grouped(plist, pdl=True)
-                if gathered is not None:
-                    dist.all_gather_into_tensor(gathered[0], gathered[1])
+            for li, (plist, gathered) in enumerate(launches):
+                if fused:
+                    writers = peer.launch(plist, gathered, li % 4, pdl=True)
+                    peer.wait(li % 4, writers)
+                else:
+                    lutgemm.lutgemv_grouped(plist, pdl=True)
+                    if gathered is not None:
+                        dist.all_gather_into_tensor(gathered[0], gathered[1])
         return one_step
 
     stream = torch.cuda.Stream(device)
@@ -275,7 +294,9 @@ def run_ours(args, rank, world, device):
                    "launch_structure": ("one grouped launch per decoder block (7 independent products); PDL chained; "
                                         + ("CUDA graph" if graphed else "eager")),
                    "l2": f"inputs larger than L2 ({total / 1e9:.1f} GB of weights per step), no flush",
-                   "parallelism": f"column-parallel x{world} + NCCL all-gather" if world > 1 else "single GPU"},
+                   "parallelism": (f"column-parallel x{world}, all-gather "
+                                   + ("fused into the kernel (peer-to-peer stores + counters)" if fused else "by NCCL"))
+                   if world > 1 else "single GPU"},
         "tokens_per_s_linears_only": round(1e3 / ms_per_step, 1),
         "gemv_per_s": round(LAYERS * 7 * 1e3 / ms_per_step, 1),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
@@ -393,6 +414,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: all-gather of the output slices fused into the kernel (peer stores) or a separate NCCL call")
     ap.add_argument("--workload", default="llama2-7b", choices=sorted(WORKLOADS),
                     help="linear set to run (default: the configuration the headline metric is quoted on)")
     args = ap.parse_args()

@@ -58,6 +58,7 @@ extern "C" {
 #define SAL_MAX_Q 8
 #define SAL_MAX_M 64
 #define SAL_MAX_GROUP 8 /* problems per grouped launch */
+#define SAL_MAX_PEERS 8 /* GPUs taking part in a fused exchange */
 
 int sal_version(void);
 const char *sal_status_string(int status);
@@ -164,6 +165,37 @@ typedef struct sal_problem {
 
 int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags,
                         void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Grouped launch with the all-gather of the output slices FUSED into the kernel (column-parallel
+ * layers over the GPUs of one node).  No counterpart in the reference, which has no tensor
+ * parallelism (model/opt.py:330-364 is a layer pipeline).  Every rank holds columns
+ * [rank*N, (rank+1)*N) of each product (so sal_problem.N is the LOCAL width) and calls this with the
+ * same shapes.  Besides writing problems[i].y, the CTA that finishes an output element stores it
+ * (plain peer-to-peer stores over NVLink, no multicast) into EVERY peer buffer at element
+ * gather_offsets[i] + rank*N + n, then adds 1 to counter `slot` of every rank's flag array
+ * (system-scope release).  `*writers_out` receives the number of arrivals THIS rank contributes
+ * per launch; with identical shapes on all ranks a rank has the complete gathered data once its
+ * counter reaches world * writers — sal_exchange_wait does that wait.
+ * peer_buffers / peer_flags: device pointers valid on this GPU for every rank's buffer (fp16) and
+ * flag array (uint32), e.g. from CUDA IPC or torch symmetric memory; flags start at zero.
+ * Use at least two slots in rotation (a slot is cleared by the wait that consumed it).  M = 1 only.
+ */
+typedef struct sal_exchange {
+    int world, rank, slot;
+    void *peer_buffers[SAL_MAX_PEERS];
+    void *peer_flags[SAL_MAX_PEERS];
+    const long long *gather_offsets; /* HOST array, one element offset per problem */
+} sal_exchange;
+
+int sal_lutgemv_grouped_exchange(const sal_problem *problems, int count, unsigned flags,
+                                 void *workspace, size_t workspace_bytes, const sal_exchange *exchange,
+                                 int *writers_out, void *stream);
+
+/* Enqueues a one-thread kernel that waits (bounded, about one second; SAL_E_TIMEOUT is recorded
+ * in the workspace status word if it gives up) until counter `slot` of this rank's flag array
+ * reaches `expected`, then clears it.  `workspace` may be NULL (no status reporting). */
+int sal_exchange_wait(void *local_flags, int slot, unsigned expected, void *workspace, void *stream);
 
 /* Introspection for tests and the benchmark: which kernel a mode-A call would
  * use (1 = tiled TMA kernel, 0 = generic) and its launch geometry. */

@@ -18,6 +18,7 @@ SAL_E_NULL, SAL_E_SHAPE, SAL_E_ALIGN, SAL_E_WORKSPACE = -1, -2, -3, -4
 SAL_E_LAUNCH, SAL_E_UNSUPPORTED, SAL_E_DEVICE, SAL_E_TIMEOUT = -5, -6, -7, -8
 SAL_ACCUMULATE, SAL_PDL, SAL_FORCE_GENERIC = 1, 2, 4
 SAL_MAX_GROUP = 8
+SAL_MAX_PEERS = 8
 SAL_MAX_M = 64
 
 _vp, _i, _u, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
@@ -26,6 +27,11 @@ _vp, _i, _u, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
 class SalProblem(ctypes.Structure):
     _fields_ = [("bw", _vp), ("alpha", _vp), ("bias", _vp), ("x", _vp), ("y", _vp),
                 ("M", _i), ("K", _i), ("N", _i), ("q", _i), ("num_groups", _i)]
+
+
+class SalExchange(ctypes.Structure):
+    _fields_ = [("world", _i), ("rank", _i), ("slot", _i), ("peer_buffers", _vp * 8), ("peer_flags", _vp * 8),
+                ("gather_offsets", ctypes.POINTER(ctypes.c_longlong))]
 
 
 class SalPlanInfo(ctypes.Structure):
@@ -47,6 +53,9 @@ SIGNATURES = {
     "sal_lutgemm_block_shift": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemm_block_shift_int8": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemv_grouped": (_i, [ctypes.POINTER(SalProblem), _i, _u, _vp, _sz, _vp]),
+    "sal_lutgemv_grouped_exchange": (_i, [ctypes.POINTER(SalProblem), _i, _u, _vp, _sz, ctypes.POINTER(SalExchange),
+                                          ctypes.POINTER(_i), _vp]),
+    "sal_exchange_wait": (_i, [_vp, _i, _u, _vp, _vp]),
     "sal_plan_shift_scale": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(SalPlanInfo)]),
     "sal_debug_set": (_i, [ctypes.c_char_p, _i]),
     # include/sal_decode_ops.h

@@ -72,6 +72,18 @@ struct TileProblem {
     int nsub_per_range;
     int ranges, splits;
     int cta_begin;
+    long long gather_off;  // fused exchange: element offset of this problem's [world][N] block in the peer buffers
+};
+
+// Fused all-gather of the output slices (column-parallel layers): every finished y element is
+// also stored into the same place of every peer's buffer, then one counter per peer is bumped.
+struct ExchangeParams {
+    int world;   // 0/1: off
+    int rank;
+    int slot;    // which counter of the flag arrays this launch signals
+    int pad_;
+    __half *base[SAL_MAX_PEERS];
+    unsigned *flags[SAL_MAX_PEERS];
 };
 
 struct TileParams {
@@ -84,6 +96,7 @@ struct TileParams {
     int accumulate;
     int ablate;  // measurement only: bit0 skip alpha loads, bit1 skip table builds, bit2 skip lookups
     int *status;
+    ExchangeParams ex;
 };
 
 // ------------------------------------------------------------------------------------------
@@ -232,6 +245,42 @@ __device__ __forceinline__ void build_tables(const __half *__restrict__ x0, cons
             }
         }
     }
+}
+
+// Fused exchange, producer side.  A finished output element is stored into every peer's gather
+// buffer with a plain peer-to-peer store (NVLink): slice `rank` of the problem's [world][N] block.
+__device__ __forceinline__ void push_to_peers(const ExchangeParams &ex, long long gather_off, int N, int n, __half v) {
+    const long long off = gather_off + (long long)ex.rank * N + n;
+    for (int t = 0; t < ex.world; ++t) ex.base[t][off] = v;  // includes this rank's own gather buffer
+}
+// After all threads of a writer CTA pushed their elements: make the stores visible system-wide,
+// then bump this launch's counter on every peer (and on this rank).  One arrival per writer CTA.
+__device__ __forceinline__ void signal_peers(const ExchangeParams &ex, int tid, int nthreads) {
+    __threadfence_system();
+    consumer_barrier(nthreads);
+    if (tid < ex.world) atomicAdd_system(ex.flags[tid] + ex.slot, 1u);
+}
+
+// Fused exchange, consumer side: waits (bounded, ~1 s) until `expected` writer CTAs of all ranks
+// have signalled counter `flag`, then clears it for the next use.  Launched between the producing
+// launch and whatever reads the gathered data on this rank.
+__global__ void exchange_wait_kernel(unsigned *flag, unsigned expected, int *status) {
+    // Let the next kernel of the stream start right away: it prefetches its weights while this
+    // thread waits for the peers, and only proceeds past its own griddepcontrol.wait once this
+    // kernel has finished.  Polling before the producing launch has finished is harmless.
+    pdl_launch_dependents();
+    if (threadIdx.x != 0) return;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= expected) break;
+        if (global_timer_ns() - t0 > 1000000000ull) {
+            if (status) atomicExch(status, SAL_E_TIMEOUT);
+            break;
+        }
+    }
+    *flag = 0u;
 }
 
 // Shared-window address at which the dynamic shared memory of a kernel without static
@@ -494,11 +543,14 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                         float v = acc[r][sub];
                         if (pr.bias) v += __half2float(pr.bias[n]);
                         if (P.accumulate) v += __half2float(yrow[n]);
-                        yrow[n] = __float2half_rn(v);
+                        const __half hv = __float2half_rn(v);
+                        yrow[n] = hv;
+                        if (ROWS == 1 && P.ex.world > 1) push_to_peers(P.ex, pr.gather_off, N, n, hv);
                     }
                 }
             }
         }
+        if (ROWS == 1 && P.ex.world > 1) signal_peers(P.ex, tid, NCW * 32);
         return;
     }
     // partial sums: [activation row][K split][N]; arrival counters: [row pair][column range]
@@ -555,12 +607,15 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                         float rsum = v[u];
                         if (pr.bias) rsum += __half2float(pr.bias[n]);
                         if (P.accumulate) rsum += __half2float(yrow[n]);
-                        yrow[n] = __float2half_rn(rsum);
+                        const __half hv = __float2half_rn(rsum);
+                        yrow[n] = hv;
+                        if (ROWS == 1 && P.ex.world > 1) push_to_peers(P.ex, pr.gather_off, N, n, hv);
                     }
                 }
             }
         }
         if (tid == 0) *counter = 0u;  // leave the scratch buffer ready for the next call
+        if (ROWS == 1 && P.ex.world > 1) signal_peers(P.ex, tid, NCW * 32);
     }
 }
 
@@ -878,7 +933,7 @@ int run_generic(int kind, const GenericParams &p, cudaStream_t stream) {
 }
 
 int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void *workspace, size_t ws_bytes,
-                    cudaStream_t stream, sal_plan_info *info_only) {
+                    cudaStream_t stream, sal_plan_info *info_only, const sal_exchange *ex = nullptr, int *writers_out = nullptr) {
     DeviceInfo *dev = nullptr;
     if (!info_only) {
         int rc = device_info(&dev);
@@ -905,6 +960,20 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     P.accumulate = (flags & SAL_ACCUMULATE) ? 1 : 0;
     P.ablate = g_ablate;
     P.status = workspace ? reinterpret_cast<int *>(workspace) : nullptr;
+    if (ex) {
+        if (ex->world < 2 || ex->world > SAL_MAX_PEERS || ex->rank < 0 || ex->rank >= ex->world || ex->slot < 0 || M != 1 ||
+            !ex->gather_offsets)
+            return SAL_E_SHAPE;
+        P.ex.world = ex->world;
+        P.ex.rank = ex->rank;
+        P.ex.slot = ex->slot;
+        for (int t = 0; t < ex->world; ++t) {
+            if (!ex->peer_buffers[t] || !ex->peer_flags[t]) return SAL_E_NULL;
+            P.ex.base[t] = reinterpret_cast<__half *>(ex->peer_buffers[t]);
+            P.ex.flags[t] = reinterpret_cast<unsigned *>(ex->peer_flags[t]);
+        }
+    }
+    int writers = 0;
 
     // CTA budget per problem, proportional to its weight volume
     double units_total = 0;
@@ -937,6 +1006,8 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         tp.ranges = pl.ranges;
         tp.splits = pl.splits;
         tp.cta_begin = cta;
+        tp.gather_off = ex ? (long long)ex->gather_offsets[i] : 0;
+        writers += pl.ranges;  // one CTA per column range stores final outputs
         if (!info_only) {
             const int erc = encode_weight_map(&P.tmap[i], sp.bw, sp.K, sp.N, sp.q);
             if (erc != SAL_OK) return erc;
@@ -952,6 +1023,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         n_off += (size_t)sp.N;
         cta += pl.ranges * pl.splits;
     }
+    if (writers_out) *writers_out = writers;
     if (info_only) {
         info_only->tiled = 1;
         info_only->ctas = cta;
@@ -1192,6 +1264,44 @@ int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags, 
     if (rc != SAL_OK) return rc;
     return run_tiled_group(problems, count, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream),
                            nullptr);
+}
+
+int sal_lutgemv_grouped_exchange(const sal_problem *problems, int count, unsigned flags, void *workspace,
+                                 size_t workspace_bytes, const sal_exchange *exchange, int *writers_out, void *stream) {
+    if (!problems || !exchange) return SAL_E_NULL;
+    if (count < 1 || count > SAL_MAX_GROUP) return SAL_E_SHAPE;
+    for (int i = 0; i < count; ++i) {
+        const sal_problem &sp = problems[i];
+        int rc = validate_common(sp.bw, sp.alpha, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q);
+        if (rc != SAL_OK) return rc;
+        if (sp.num_groups <= 0 || sp.K % sp.num_groups != 0) return SAL_E_SHAPE;
+        if (sp.q != problems[0].q || sp.M != 1) return SAL_E_UNSUPPORTED;
+        if (!tiled_eligible(sp.bw, sp.alpha, sp.bias, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q, sp.num_groups))
+            return SAL_E_UNSUPPORTED;
+    }
+    DeviceInfo *dev = nullptr;
+    int rc = device_info(&dev);
+    if (rc != SAL_OK) return rc;
+    return run_tiled_group(problems, count, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream),
+                           nullptr, exchange, writers_out);
+}
+
+int sal_exchange_wait(void *local_flags, int slot, unsigned expected, void *workspace, void *stream) {
+    if (!local_flags) return SAL_E_NULL;
+    if (slot < 0) return SAL_E_SHAPE;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cuda_ok(cudaLaunchKernelEx(&cfg, exchange_wait_kernel, reinterpret_cast<unsigned *>(local_flags) + slot, expected,
+                                      reinterpret_cast<int *>(workspace)))
+               ? SAL_OK
+               : SAL_E_LAUNCH;
 }
 
 // ---- entry point that allocates nothing ---------------------------------------------------
