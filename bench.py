@@ -155,7 +155,15 @@ def run_ours(args, rank, world, device):
     if fused:
         from shiftaddllm_b200.exchange import PeerExchange
 
-        peer = PeerExchange.symmetric(n_out, nslots=4)
+        try:
+            peer = PeerExchange.symmetric(n_out, nslots=4)
+            ok = torch.ones(1, device=device)
+        except Exception as exc:  # noqa: BLE001 - no peer-mappable memory on this box: use NCCL on every rank
+            print(f"[bench] symmetric memory unavailable ({type(exc).__name__}: {exc}); using the NCCL exchange", file=sys.stderr)
+            ok = torch.zeros(1, device=device)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)   # all ranks take the same path
+        fused = bool(ok.item())
+    if fused:
         y_full = peer.buffer
     else:
         y_full = torch.zeros(n_out, dtype=torch.float16, device=device) if world > 1 else None

@@ -161,6 +161,8 @@ typedef struct sal_problem {
     const void *x;     /* fp16 [M][K] */
     void *y;           /* fp16 [M][N] */
     int M, K, N, q, num_groups;
+    const void *x_mul; /* optional fp16 [M][K] (NULL = unused): the activation becomes silu(x) * x_mul,
+                          i.e. x = gate, x_mul = up of a SwiGLU block feeding this (down) projection */
 } sal_problem;
 
 int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags,
@@ -212,9 +214,8 @@ int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_in
 /* Measurement hook, process-wide, not for production use.  Keys: "stages" caps the
  * depth of the shared-memory ring of the tiled kernel (0 = as deep as fits);
  * "budget_pct" scales the number of SMs the planner sizes its grid for
- * (100 = one CTA per SM, 200 = two, 0 = automatic); "ncw" 8 or 16 picks the CTA
- * shape (8 consumer warps and two CTAs per SM, or 16 and one); "full_sm" lets
- * the 8-warp CTA use a whole SM's shared memory; "abs" 0/1 forces the table
+ * (100 = one CTA per SM, 200 = two, 0 = automatic); "full_sm" lets a CTA use a
+ * whole SM's shared memory (one CTA per SM, deeper ring); "abs" 0/1 forces the table
  * addressing variant; "ablate" bit0/1/2 skips alpha loads / table builds /
  * lookups (results are then meaningless; used to time the parts). */
 int sal_debug_set(const char *key, int value);

@@ -26,7 +26,7 @@ _vp, _i, _u, _sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
 
 class SalProblem(ctypes.Structure):
     _fields_ = [("bw", _vp), ("alpha", _vp), ("bias", _vp), ("x", _vp), ("y", _vp),
-                ("M", _i), ("K", _i), ("N", _i), ("q", _i), ("num_groups", _i)]
+                ("M", _i), ("K", _i), ("N", _i), ("q", _i), ("num_groups", _i), ("x_mul", _vp)]
 
 
 class SalExchange(ctypes.Structure):

@@ -62,6 +62,7 @@ struct TileProblem {
     const __half *alpha;
     const __half *bias;
     const __half *x;
+    const __half *x_mul;  // optional: the activation is silu(x) * x_mul (SwiGLU feeding a down projection)
     __half *y;
     float *partials;     // [splits][N]
     unsigned *counters;  // [ranges]
@@ -205,9 +206,10 @@ struct TileCfg {
 // entries (entry >> 3 = hg).  Bank of every store = lane.  ROWS = 1: fp32 entries of activation
 // row x0.  ROWS = 2: half2 entries, low half = row x0, high half = row x1 (sums are formed in
 // fp32 and rounded once).
-template <int NCW, int ROWS>
-__device__ __forceinline__ void build_tables(const __half *__restrict__ x0, const __half *__restrict__ x1,
-                                             uint32_t lut_half, int warp, int lane) {
+template <int NCW, int ROWS, bool SWIGLU>
+__device__ __forceinline__ void build_tables_impl(const __half *__restrict__ x0, const __half *__restrict__ x1,
+                                                  const __half *__restrict__ m0, const __half *__restrict__ m1,
+                                                  uint32_t lut_half, int warp, int lane) {
     float xf[ROWS][8];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
@@ -218,6 +220,18 @@ __device__ __forceinline__ void build_tables(const __half *__restrict__ x0, cons
             const float2 f = __half22float2(h[i]);
             xf[r][2 * i] = f.x;
             xf[r][2 * i + 1] = f.y;
+        }
+        if (SWIGLU) {
+            // fused SwiGLU: the activation is silu(gate) * up, rounded to fp16 after each step exactly as
+            // the separate element-wise kernel (and torch's fp16 ops) would produce it
+            const uint4 mraw = __ldg(reinterpret_cast<const uint4 *>(r == 0 ? m0 : m1) + lane);
+            const __half *mh = reinterpret_cast<const __half *>(&mraw);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float g = xf[r][i];
+                const float sg = __half2float(__float2half_rn(g / (1.f + __expf(-g))));
+                xf[r][i] = __half2float(__float2half_rn(sg * __half2float(mh[i])));
+            }
         }
     }
     float low[ROWS][8];
@@ -291,8 +305,11 @@ __global__ void exchange_wait_kernel(unsigned *flag, unsigned expected, int *sta
 constexpr uint32_t SMEM_DYNAMIC_BASE = 1024;
 
 // ROWS = 1: the M = 1 kernel.  ROWS = 2: small-batch variant, blockIdx.y = pair of activation
-// rows; the same weight tile serves both rows through half2 table entries.
-template <int Q, int NCW, bool ABS, int ROWS>
+// rows; the same weight tile serves both rows through half2 table entries.  SWIGLU: the activation
+// is silu(x) * x_mul, formed while the tables are built (a separate instantiation, so that the
+// extra registers of that prologue do not weigh on the ordinary kernel).  EXCH: the fused all-gather
+// epilogue (peer stores + counters), likewise its own instantiation.
+template <int Q, int NCW, bool ABS, int ROWS, bool SWIGLU, bool EXCH>
 __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     lutgemv_tiled_kernel(const __grid_constant__ TileParams P) {
     using C = TileCfg<Q, NCW>;
@@ -441,7 +458,13 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     auto process_block = [&](int kb, auto par_tag) {
         constexpr int PAR = decltype(par_tag)::value;
         if (!(P.ablate & 2))
-            build_tables<NCW, ROWS>(xrow0 + (size_t)kb * KB_FEATS, xrow1 + (size_t)kb * KB_FEATS, lut_s + PAR * 128, warp, lane);
+        {
+            const size_t ko = (size_t)kb * KB_FEATS;
+            // x_mul row = x_mul + (the same element offset the x row has)
+            const __half *m0 = SWIGLU ? pr.x_mul + (xrow0 - pr.x) + ko : nullptr;
+            const __half *m1 = SWIGLU ? pr.x_mul + (xrow1 - pr.x) + ko : nullptr;
+            build_tables_impl<NCW, ROWS, SWIGLU>(xrow0 + ko, xrow1 + ko, m0, m1, lut_s + PAR * 128, warp, lane);
+        }
         consumer_barrier(NCW * 32);
         // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
         // unrolling it over the column tiles overflows the instruction cache.  acc[] is then
@@ -545,12 +568,19 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                         if (P.accumulate) v += __half2float(yrow[n]);
                         const __half hv = __float2half_rn(v);
                         yrow[n] = hv;
-                        if (ROWS == 1 && P.ex.world > 1) push_to_peers(P.ex, pr.gather_off, N, n, hv);
                     }
                 }
             }
         }
-        if (ROWS == 1 && P.ex.world > 1) signal_peers(P.ex, tid, NCW * 32);
+        if (EXCH && P.ex.world > 1) {
+            // second pass on purpose (each thread re-reads what it just wrote): keeps the peer pointers out of
+            // the registers of the loop above
+            for (int sub = 0; sub < nsub; ++sub) {
+                const int n = (sub_begin + sub) * CW + col;
+                if (n < N) push_to_peers(P.ex, pr.gather_off, N, n, pr.y[n]);
+            }
+            signal_peers(P.ex, tid, NCW * 32);
+        }
         return;
     }
     // partial sums: [activation row][K split][N]; arrival counters: [row pair][column range]
@@ -609,13 +639,18 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                         if (P.accumulate) rsum += __half2float(yrow[n]);
                         const __half hv = __float2half_rn(rsum);
                         yrow[n] = hv;
-                        if (ROWS == 1 && P.ex.world > 1) push_to_peers(P.ex, pr.gather_off, N, n, hv);
                     }
                 }
             }
         }
         if (tid == 0) *counter = 0u;  // leave the scratch buffer ready for the next call
-        if (ROWS == 1 && P.ex.world > 1) signal_peers(P.ex, tid, NCW * 32);
+        if (EXCH && P.ex.world > 1) {
+            for (int sub = 0; sub < nsub; ++sub) {
+                const int n = (sub_begin + sub) * CW + col;
+                if (n < N) push_to_peers(P.ex, pr.gather_off, N, n, pr.y[n]);
+            }
+            signal_peers(P.ex, tid, NCW * 32);
+        }
     }
 }
 
@@ -814,7 +849,6 @@ int g_full_sm = 0;  // measurement hook: let one CTA use a whole SM's shared mem
 // Ring depth: as many stages as fit in half of an SM's shared memory next to the
 // 64 KB of tables, so that two CTAs (of this kernel or of the next one in the
 // stream) are resident together.
-int g_ncw = 8;  // consumer warps per CTA: 8 (two CTAs per SM) or 16 (one CTA per SM, whole shared memory)
 
 int choose_stages(int q, int ncw, int smem_optin, int *smem_bytes) {
     const int sb = stage_bytes_for(q, ncw);
@@ -858,9 +892,9 @@ int encode_weight_map(CUtensorMap *out, const void *bw, int K, int N, int q) {
     return r == CUDA_SUCCESS ? SAL_OK : SAL_E_LAUNCH;
 }
 
-template <int Q, int NCW, bool ABS, int ROWS>
+template <int Q, int NCW, bool ABS, int ROWS, bool SWIGLU, bool EXCH = false>
 cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int row_groups, int smem, unsigned flags, cudaStream_t stream) {
-    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS, ROWS>;
+    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS, ROWS, SWIGLU, EXCH>;
     static int configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -884,18 +918,24 @@ cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int row_groups, 
     return cudaLaunchKernelEx(&cfg, kern, P);
 }
 
+template <int Q, bool ABS>
+cudaError_t launch_tiled_abs(const TileParams &P, int rows, int row_groups, bool swiglu, int ctas, int smem, unsigned flags,
+                             cudaStream_t stream) {
+    if (P.ex.world > 1)   // fused exchange: M = 1, plain activations (checked by the caller)
+        return launch_tiled_variant<Q, 8, ABS, 1, false, true>(P, ctas, 1, smem, flags, stream);
+    if (rows == 2)
+        return swiglu ? launch_tiled_variant<Q, 8, ABS, 2, true>(P, ctas, row_groups, smem, flags, stream)
+                      : launch_tiled_variant<Q, 8, ABS, 2, false>(P, ctas, row_groups, smem, flags, stream);
+    return swiglu ? launch_tiled_variant<Q, 8, ABS, 1, true>(P, ctas, 1, smem, flags, stream)
+                  : launch_tiled_variant<Q, 8, ABS, 1, false>(P, ctas, 1, smem, flags, stream);
+}
+
 template <int Q>
-cudaError_t launch_tiled(const TileParams &P, int ncw, int ctas, int rows, int row_groups, int smem, unsigned flags,
+cudaError_t launch_tiled(const TileParams &P, int ctas, int rows, int row_groups, bool swiglu, int smem, unsigned flags,
                          bool abs_ok, cudaStream_t stream) {
     const bool use_abs = g_abs_override >= 0 ? (g_abs_override != 0) : abs_ok;
-    if (rows == 2)
-        return use_abs ? launch_tiled_variant<Q, 8, true, 2>(P, ctas, row_groups, smem, flags, stream)
-                       : launch_tiled_variant<Q, 8, false, 2>(P, ctas, row_groups, smem, flags, stream);
-    if (ncw > 8)
-        return use_abs ? launch_tiled_variant<Q, 16, true, 1>(P, ctas, 1, smem, flags, stream)
-                       : launch_tiled_variant<Q, 16, false, 1>(P, ctas, 1, smem, flags, stream);
-    return use_abs ? launch_tiled_variant<Q, 8, true, 1>(P, ctas, 1, smem, flags, stream)
-                   : launch_tiled_variant<Q, 8, false, 1>(P, ctas, 1, smem, flags, stream);
+    return use_abs ? launch_tiled_abs<Q, true>(P, rows, row_groups, swiglu, ctas, smem, flags, stream)
+                   : launch_tiled_abs<Q, false>(P, rows, row_groups, swiglu, ctas, smem, flags, stream);
 }
 
 bool tiled_eligible(const void *bw, const void *alpha, const void *bias, const void *x, const void *y, int M, int K,
@@ -948,7 +988,8 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const int M = problems[0].M;
     const int rows = M > 1 ? 2 : 1;
     const int row_groups = (M + rows - 1) / rows;
-    const int ncw = (rows == 1 && g_ncw > 8) ? 16 : 8;
+    const int ncw = 8;   // consumer warps per CTA (a 16-warp, one-CTA-per-SM shape was measured and is not faster)
+    const bool swiglu = problems[0].x_mul != nullptr;   // all problems of a launch must agree
     const int cw = ncw * 32;
     const int ctas_per_sm = ncw > 8 ? 1 : 2;
     const int stages = choose_stages(q, ncw, optin, &smem);
@@ -995,6 +1036,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         tp.alpha = reinterpret_cast<const __half *>(sp.alpha);
         tp.bias = reinterpret_cast<const __half *>(sp.bias);
         tp.x = reinterpret_cast<const __half *>(sp.x);
+        tp.x_mul = reinterpret_cast<const __half *>(sp.x_mul);
         tp.y = reinterpret_cast<__half *>(sp.y);
         tp.K = sp.K;
         tp.N = sp.N;
@@ -1051,10 +1093,10 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const bool abs_ok = dev->smem_base == (int)SMEM_DYNAMIC_BASE;
     cudaError_t e;
     switch (q) {
-        case 1: e = launch_tiled<1>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
-        case 2: e = launch_tiled<2>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
-        case 3: e = launch_tiled<3>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
-        default: e = launch_tiled<4>(P, ncw, cta, rows, row_groups, smem, flags, abs_ok, stream); break;
+        case 1: e = launch_tiled<1>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
+        case 2: e = launch_tiled<2>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
+        case 3: e = launch_tiled<3>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
+        default: e = launch_tiled<4>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
     }
     return cuda_ok(e) ? SAL_OK : SAL_E_LAUNCH;
 }
@@ -1119,7 +1161,6 @@ int sal_debug_set(const char *key, int value) {
     else if (eq("abs")) g_abs_override = value;
     else if (eq("ablate")) g_ablate = value;
     else if (eq("full_sm")) g_full_sm = value;
-    else if (eq("ncw")) g_ncw = value;
     else if (eq("budget_pct")) g_budget_pct = value > 0 ? value : 0;
     else return SAL_E_UNSUPPORTED;
     return SAL_OK;
@@ -1256,6 +1297,8 @@ int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags, 
         if (rc != SAL_OK) return rc;
         if (sp.num_groups <= 0 || sp.K % sp.num_groups != 0) return SAL_E_SHAPE;
         if (sp.q != problems[0].q || sp.M != problems[0].M) return SAL_E_UNSUPPORTED;
+        if (sp.x_mul && !aligned(sp.x_mul, 16)) return SAL_E_ALIGN;
+        if ((sp.x_mul != nullptr) != (problems[0].x_mul != nullptr)) return SAL_E_UNSUPPORTED;
         if (!tiled_eligible(sp.bw, sp.alpha, sp.bias, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q, sp.num_groups))
             return SAL_E_UNSUPPORTED;
     }
@@ -1275,7 +1318,7 @@ int sal_lutgemv_grouped_exchange(const sal_problem *problems, int count, unsigne
         int rc = validate_common(sp.bw, sp.alpha, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q);
         if (rc != SAL_OK) return rc;
         if (sp.num_groups <= 0 || sp.K % sp.num_groups != 0) return SAL_E_SHAPE;
-        if (sp.q != problems[0].q || sp.M != 1) return SAL_E_UNSUPPORTED;
+        if (sp.q != problems[0].q || sp.M != 1 || sp.x_mul != nullptr) return SAL_E_UNSUPPORTED;
         if (!tiled_eligible(sp.bw, sp.alpha, sp.bias, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q, sp.num_groups))
             return SAL_E_UNSUPPORTED;
     }

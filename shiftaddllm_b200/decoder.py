@@ -77,10 +77,11 @@ class _Block:
                 "gate_proj": self.gate_proj, "up_proj": self.up_proj, "down_proj": self.down_proj}
 
 
-def _group(lins, x, outs, pdl=True):
-    """One grouped LUT-GEMV launch: every layer of `lins` applied to the same activation row."""
+def _group(lins, x, outs, pdl=True, x_mul=None):
+    """One grouped LUT-GEMV launch: every layer of `lins` applied to the same activation row
+    (`x_mul` given: to silu(x) * x_mul, formed inside the kernel)."""
     probs = [dict(output=o, bWeight=l.binaryWeight, alpha=l.alpha, bias=l.bias, d_input=x, mSize=l.N, kSize=l.K,
-                  nb=l.wbit, num_groups=l.alpha.shape[0]) for l, o in zip(lins, outs)]
+                  nb=l.wbit, num_groups=l.alpha.shape[0], d_input_mul=x_mul) for l, o in zip(lins, outs)]
     lutgemm.lutgemv_grouped(probs, pdl=pdl)
 
 
@@ -161,7 +162,8 @@ class BcqLlamaDecoder:
 
     def _step_fused(self):
         """Same step with the fused helpers of include/sal_decode_ops.h: per block 4 LUT-GEMV
-        launches + 5 helper launches (residual+RMSNorm x2, RoPE+cache write, attention, SiLU*up)."""
+        launches + 4 helper launches (residual+RMSNorm x2, RoPE+cache write, attention); SiLU(gate)*up is
+        computed inside down_proj's table build."""
         s = self.shape
         hd, kvh = s.head_dim, s.kv_heads
         scale = 1.0 / math.sqrt(hd)
@@ -177,8 +179,7 @@ class BcqLlamaDecoder:
             _group((blk.o_proj,), self._attn, (self._o,))
             decode_ops.residual_rmsnorm(x, self._o, blk.post_norm, hn, x, s.eps)
             _group((blk.gate_proj, blk.up_proj), hn, (self._gate, self._up))
-            decode_ops.silu_mul(self._gate, self._up, self._act)
-            _group((blk.down_proj,), self._act, (self._down,))
+            _group((blk.down_proj,), self._gate, (self._down,), x_mul=self._up)   # SiLU(gate)*up formed in the table build
             delta = self._down
         decode_ops.residual_rmsnorm(x, delta, self.final_norm, hn, x, s.eps)
         self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))

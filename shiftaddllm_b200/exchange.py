@@ -75,7 +75,7 @@ class PeerExchange:
             arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
                                      bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
                                      p["output"].data_ptr(), 1, int(p["kSize"]), int(p["mSize"]), int(p["nb"]),
-                                     int(p["num_groups"]))
+                                     int(p["num_groups"]), None)
             n_total += int(p["mSize"])
         offs = (ctypes.c_longlong * len(problems))(*[int(o) for o in gather_offsets])
         ex = _lib.SalExchange()

@@ -135,7 +135,8 @@ def lutgemv_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb, num_g
 def lutgemv_grouped(problems, *, pdl=False, accumulate=False):
     """Several independent mode-A products in one launch.  ``problems`` is a list
     of dicts with keys output, bWeight, alpha, bias (or None), d_input,
-    mSize, kSize, nb, num_groups."""
+    mSize, kSize, nb, num_groups and optionally d_input_mul (the activation is then
+    silu(d_input) * d_input_mul, computed while the tables are built)."""
     lib = _lib.load()
     if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
         raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
@@ -150,9 +151,15 @@ def lutgemv_grouped(problems, *, pdl=False, accumulate=False):
         n, k = int(p["mSize"]), int(p["kSize"])
         m = _rows(p["output"], p["d_input"], n, k)
         bias = p.get("bias")
+        mul = p.get("d_input_mul")      # optional: the activation is silu(d_input) * d_input_mul
+        if mul is not None:
+            _req(mul, torch.float16, "d_input_mul")
+            if mul.numel() != p["d_input"].numel():
+                raise RuntimeError("d_input_mul must have the shape of d_input")
         arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
                                  bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
-                                 p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]))
+                                 p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]),
+                                 mul.data_ptr() if mul is not None else None)
         n_total += n
     flags = (_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
     with torch.cuda.device(dev):

@@ -171,6 +171,32 @@ def test_grouped_launch_qkv():
     assert_status_clean()
 
 
+def test_fused_swiglu_input():
+    """down_proj with x = silu(gate) * up formed inside the table build equals the two-step path."""
+    import torch.nn.functional as F
+
+    from shiftaddllm_b200 import decode_ops
+
+    for m in (1, 3):
+        layer = synth.make_layer(2048, 512, 3, 128, M=m, packed_draw=True)
+        g = torch.Generator().manual_seed(9)
+        gate, up = torch.randn(m, 2048, generator=g).half().cuda(), torch.randn(m, 2048, generator=g).half().cuda()
+        bw, al = dev(layer.bWeight), dev(layer.alpha)
+        y_fused = torch.empty(m, 512, dtype=torch.float16, device="cuda")
+        lutgemm.lutgemv_grouped([dict(output=y_fused, bWeight=bw, alpha=al, bias=None, d_input=gate, d_input_mul=up,
+                                      mSize=512, kSize=2048, nb=3, num_groups=16)])
+        act = torch.empty_like(gate)
+        decode_ops.silu_mul(gate, up, act)
+        y_two = torch.empty_like(y_fused)
+        lutgemm.lutgemv_grouped([dict(output=y_two, bWeight=bw, alpha=al, bias=None, d_input=act, mSize=512, kSize=2048,
+                                      nb=3, num_groups=16)])
+        torch.cuda.synchronize()
+        assert torch.equal(y_fused, y_two)
+        w = o.dequant_mode_a(layer.bWeight.numpy(), layer.alpha.numpy())
+        ref = o.linear_fp32((F.silu(gate.float()) * up.float()).cpu().numpy(), w)
+        assert o.max_rel_err(y_fused.float().cpu().numpy(), ref) <= TOL
+
+
 def test_hand_checkable():
     k, n, q = 512, 256, 2
     bw = torch.full((k // 32, q, n), -1, dtype=torch.int32, device="cuda")          # every bit set: all +1
