@@ -678,6 +678,9 @@ struct GenericParams {
     int gs;       // mode B: columns per group
     int num_apot;
     int accumulate;
+    int ksplit;          // K splits (grid.z); > 1 needs the scratch buffer below
+    float *partials;     // [M][ksplit][N]
+    unsigned *counters;  // [M][column blocks]
 };
 
 template <int KIND>
@@ -702,9 +705,31 @@ __global__ void __launch_bounds__(128) lutgemv_generic_kernel(const GenericParam
     const int m = blockIdx.y;
     const __half *xrow = p.x + (size_t)m * p.K;
     const int kwords = p.K / 32;
+    const int kblocks = (kwords + KB_WORDS - 1) / KB_WORDS;
+    const int split = blockIdx.z;
+    const int kb_begin = (int)(((long long)split * kblocks) / p.ksplit);
+    const int kb_end = (int)(((long long)(split + 1) * kblocks) / p.ksplit);
     float acc = 0.f;
-    for (int kb = 0; kb * KB_WORDS < kwords; ++kb) {
+    // Block modes: the multipliers of one K block for this CTA's column groups are decoded once into
+    // shared memory (32 chunks x q planes x up to 17 groups) instead of once per lookup.
+    constexpr int MT_Q = 4, MT_G = 17;
+    __shared__ float mult[(KIND >= B_F16) ? 32 : 1][(KIND >= B_F16) ? MT_Q : 1][(KIND >= B_F16) ? MT_G : 1];
+    const int ng_first = (KIND >= B_F16) ? (blockIdx.x * 128) / p.gs : 0;
+    const int ng_last = (KIND >= B_F16) ? (min(blockIdx.x * 128 + 127, p.N - 1)) / p.gs : 0;
+    const int ng_cnt = ng_last - ng_first + 1;
+    const bool use_mult_table = (KIND >= B_F16) && p.q <= MT_Q && ng_cnt <= MT_G;
+    for (int kb = kb_begin; kb < kb_end; ++kb) {
         __syncthreads();
+        if (use_mult_table) {
+            const int total = 32 * p.q * ng_cnt;
+            for (int e = tid; e < total; e += 128) {
+                const int g = e % ng_cnt, b = (e / ng_cnt) % p.q, c = e / (ng_cnt * p.q);
+                const int cg = kb * 32 + c;   // global chunk index
+                float m = 0.f;
+                if (cg * 8 < p.K) m = block_multiplier<KIND>(p.alpha, ((size_t)cg * p.q + b) * p.ngroups + ng_first + g, p.num_apot);
+                mult[(KIND >= B_F16) ? c : 0][(KIND >= B_F16) ? b : 0][(KIND >= B_F16) ? g : 0] = m;
+            }
+        }
         {
             const int chunk = tid >> 2;
             const int k0 = kb * KB_FEATS + chunk * 8;
@@ -752,20 +777,57 @@ __global__ void __launch_bounds__(128) lutgemv_generic_kernel(const GenericParam
                         const uint32_t w = p.bw[((size_t)kk * p.q + b) * p.N + n];
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
-                            const size_t aidx = ((size_t)(4 * kk + j) * p.q + b) * p.ngroups + ng;
-                            acc += block_multiplier<KIND>(p.alpha, aidx, p.num_apot) * lut[4 * wi + j][(w >> (8 * j)) & 255u];
+                            float mlt;
+                            if (use_mult_table) {
+                                mlt = mult[4 * wi + j][b][ng - ng_first];
+                            } else {
+                                const size_t aidx = ((size_t)(4 * kk + j) * p.q + b) * p.ngroups + ng;
+                                mlt = block_multiplier<KIND>(p.alpha, aidx, p.num_apot);
+                            }
+                            acc += mlt * lut[4 * wi + j][(w >> (8 * j)) & 255u];
                         }
                     }
                 }
             }
         }
     }
-    if (n < p.N) {
-        float v = acc;
-        if (p.bias) v += __half2float(p.bias[n]);
-        __half *yp = p.y + (size_t)m * p.N + n;
-        if (p.accumulate) v += __half2float(*yp);
-        *yp = __float2half_rn(v);
+    if (p.ksplit == 1) {
+        if (n < p.N) {
+            float v = acc;
+            if (p.bias) v += __half2float(p.bias[n]);
+            __half *yp = p.y + (size_t)m * p.N + n;
+            if (p.accumulate) v += __half2float(*yp);
+            *yp = __float2half_rn(v);
+        }
+        return;
+    }
+    // deterministic split-K, same scheme as the tiled kernel: partial sums to the scratch buffer,
+    // the last CTA of a (row, column block) to arrive adds them up in ascending split order
+    __shared__ int s_last;
+    float *prow = p.partials + ((size_t)m * p.ksplit) * p.N;
+    if (n < p.N) __stcg(prow + (size_t)split * p.N + n, acc);
+    __threadfence();
+    __syncthreads();
+    unsigned *counter = p.counters + (size_t)m * gridDim.x + blockIdx.x;
+    if (tid == 0) s_last = (atomicAdd(counter, 1u) == (unsigned)(p.ksplit - 1));
+    __syncthreads();
+    if (s_last) {
+        __threadfence();
+        if (n < p.N) {
+            float v = 0.f;
+            for (int s0 = 0; s0 < p.ksplit; s0 += 8) {
+                float t[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) t[i] = (s0 + i < p.ksplit) ? __ldcg(prow + (size_t)(s0 + i) * p.N + n) : 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v += t[i];
+            }
+            if (p.bias) v += __half2float(p.bias[n]);
+            __half *yp = p.y + (size_t)m * p.N + n;
+            if (p.accumulate) v += __half2float(*yp);
+            *yp = __float2half_rn(v);
+        }
+        if (tid == 0) *counter = 0u;
     }
 }
 
@@ -960,8 +1022,24 @@ int validate_common(const void *bw, const void *alpha, const void *x, const void
     return SAL_OK;
 }
 
-int run_generic(int kind, const GenericParams &p, cudaStream_t stream) {
-    dim3 grid((unsigned)((p.N + 127) / 128), (unsigned)p.M);
+int run_generic(int kind, GenericParams p, void *workspace, size_t ws_bytes, cudaStream_t stream) {
+    const int col_blocks = (p.N + 127) / 128;
+    const int kblocks = (p.K / 32 + KB_WORDS - 1) / KB_WORDS;
+    // K splits: aim at about four CTAs per SM; needs the scratch buffer (counters and partial sums)
+    p.ksplit = 1;
+    DeviceInfo *dev = nullptr;
+    if (workspace && device_info(&dev) == SAL_OK) {
+        int want = (4 * dev->sms + col_blocks * p.M - 1) / (col_blocks * p.M);
+        if (want > kblocks) want = kblocks;
+        if (want > MAX_SPLIT) want = MAX_SPLIT;
+        const size_t need = WS_PARTIAL_OFFSET + (size_t)p.M * (size_t)p.N * MAX_SPLIT * sizeof(float);
+        if (want > 1 && col_blocks * p.M <= WS_MAX_COUNTERS && ws_bytes >= need) {
+            p.ksplit = want;
+            p.counters = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(workspace) + WS_HEADER_BYTES);
+            p.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + WS_PARTIAL_OFFSET);
+        }
+    }
+    dim3 grid((unsigned)col_blocks, (unsigned)p.M, (unsigned)p.ksplit);
     switch (kind) {
         case A_ROW_F16: lutgemv_generic_kernel<A_ROW_F16><<<grid, 128, 0, stream>>>(p); break;
         case A_ROW_HALVING: lutgemv_generic_kernel<A_ROW_HALVING><<<grid, 128, 0, stream>>>(p); break;
@@ -1211,14 +1289,12 @@ int sal_lutgemv_shift_scale(const void *bw, const void *alpha, const void *bias,
     p.y = reinterpret_cast<__half *>(y);
     p.M = M; p.K = K; p.N = N; p.q = q; p.g = g;
     p.accumulate = (flags & SAL_ACCUMULATE) ? 1 : 0;
-    return run_generic(A_ROW_F16, p, s);
+    return run_generic(A_ROW_F16, p, workspace, workspace_bytes, s);
 }
 
 int sal_lutgemv_compute(const void *bw, const void *alpha, const void *q_bias, const void *bias, const void *x, void *y,
                         int M, int K, int N, int q, int num_groups, unsigned flags, void *workspace,
                         size_t workspace_bytes, void *stream) {
-    (void)workspace;
-    (void)workspace_bytes;
     int rc = validate_common(bw, alpha, x, y, M, K, N, q);
     if (rc != SAL_OK) return rc;
     if (!q_bias) return SAL_E_NULL;
@@ -1237,11 +1313,12 @@ int sal_lutgemv_compute(const void *bw, const void *alpha, const void *q_bias, c
     p.y = reinterpret_cast<__half *>(y);
     p.M = M; p.K = K; p.N = N; p.q = q; p.g = g;
     p.accumulate = (flags & SAL_ACCUMULATE) ? 1 : 0;
-    return run_generic(A_ROW_HALVING, p, reinterpret_cast<cudaStream_t>(stream));
+    return run_generic(A_ROW_HALVING, p, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 static int block_entry(int kind, const void *bw, const void *alpha, const void *bias, const void *x, void *y, int M,
-                       int K, int N, int q, int num_groups, int num_apot, unsigned flags, void *stream) {
+                       int K, int N, int q, int num_groups, int num_apot, unsigned flags, void *workspace,
+                       size_t workspace_bytes, void *stream) {
     int rc = validate_common(bw, alpha, x, y, M, K, N, q);
     if (rc != SAL_OK) return rc;
     if (num_groups <= 0 || N % num_groups != 0) return SAL_E_SHAPE;
@@ -1261,30 +1338,24 @@ static int block_entry(int kind, const void *bw, const void *alpha, const void *
     p.gs = N / num_groups;
     p.num_apot = num_apot;
     p.accumulate = (flags & SAL_ACCUMULATE) ? 1 : 0;
-    return run_generic(kind, p, reinterpret_cast<cudaStream_t>(stream));
+    return run_generic(kind, p, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int sal_lutgemm_block(const void *bw, const void *alpha, const void *bias, const void *x, void *y, int M, int K, int N,
                       int q, int num_groups, unsigned flags, void *workspace, size_t workspace_bytes, void *stream) {
-    (void)workspace;
-    (void)workspace_bytes;
-    return block_entry(B_F16, bw, alpha, bias, x, y, M, K, N, q, num_groups, 0, flags, stream);
+    return block_entry(B_F16, bw, alpha, bias, x, y, M, K, N, q, num_groups, 0, flags, workspace, workspace_bytes, stream);
 }
 
 int sal_lutgemm_block_shift(const void *bw, const void *alpha_u16, const void *bias, const void *x, void *y, int M,
                             int K, int N, int q, int num_groups, unsigned flags, void *workspace,
                             size_t workspace_bytes, void *stream) {
-    (void)workspace;
-    (void)workspace_bytes;
-    return block_entry(B_U16, bw, alpha_u16, bias, x, y, M, K, N, q, num_groups, 0, flags, stream);
+    return block_entry(B_U16, bw, alpha_u16, bias, x, y, M, K, N, q, num_groups, 0, flags, workspace, workspace_bytes, stream);
 }
 
 int sal_lutgemm_block_shift_int8(const void *bw, const void *alpha_i8, const void *bias, const void *x, void *y, int M,
                                  int K, int N, int q, int num_groups, int num_apot, unsigned flags, void *workspace,
                                  size_t workspace_bytes, void *stream) {
-    (void)workspace;
-    (void)workspace_bytes;
-    return block_entry(B_I8, bw, alpha_i8, bias, x, y, M, K, N, q, num_groups, num_apot, flags, stream);
+    return block_entry(B_I8, bw, alpha_i8, bias, x, y, M, K, N, q, num_groups, num_apot, flags, workspace, workspace_bytes, stream);
 }
 
 int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags, void *workspace,
