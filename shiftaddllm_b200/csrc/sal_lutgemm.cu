@@ -870,13 +870,15 @@ int device_info(DeviceInfo **out) {
 inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 
+int g_force_per = 0, g_force_splits = 0;  // measurement hooks: override the planner's choice
+
 struct Plan {
     int ranges, splits, nsub_per_range, nsub_total, kblocks;
 };
 
 // Chooses column ranges x K splits for one problem.  `slots` is the number of CTAs of this
 // problem that can be resident at once (its share of SMs x CTAs per SM).  Work unit = one
-// 256-feature K block x one column tile; building the tables of a K block costs about 0.45
+// 256-feature K block x one column tile; building the tables of a K block costs about 0.25
 // units; CTAs beyond `slots` run as later waves and restart the pipeline.
 Plan plan_problem(int K, int N, int slots, bool allow_split, int cw) {
     Plan best{};
@@ -884,14 +886,17 @@ Plan plan_problem(int K, int N, int slots, bool allow_split, int cw) {
     const int kblocks = K / KB_FEATS;
     double best_cost = 1e30;
     for (int per = 1; per <= MAX_SUB && per <= nsub_total; ++per) {
+        if (g_force_per > 0 && per != (g_force_per < nsub_total ? g_force_per : nsub_total)) continue;
         const int ranges = (nsub_total + per - 1) / per;
         const int smax = allow_split ? (kblocks < MAX_SPLIT ? kblocks : MAX_SPLIT) : 1;
         for (int splits = 1; splits <= smax; ++splits) {
+            if (g_force_splits > 0 && allow_split && splits != (g_force_splits < smax ? g_force_splits : smax)) continue;
             const int ctas = ranges * splits;
             const int kb_per = (kblocks + splits - 1) / splits;
             const int waves = (ctas + slots - 1) / slots;
-            double cost = waves * (kb_per * (per + 0.45)) + 2.0 * (waves - 1);
-            cost += 0.02 * splits + (splits > 1 ? 0.5 + 0.15 * ((per + 3) / 4) * ((splits + 15) / 16) : 0.0);  // reduction tail
+            // calibrated on a sweep of (per, splits) over the four launch shapes of a LLaMA-2-7B block
+            double cost = waves * (kb_per * (per + 0.25)) + 2.0 * (waves - 1);
+            cost += splits > 1 ? 0.5 + 0.05 * splits : 0.0;  // reduction tail grows with the number of partial sums
             if (cost < best_cost) {
                 best_cost = cost;
                 best = Plan{ranges, splits, per, nsub_total, kblocks};
@@ -1239,6 +1244,8 @@ int sal_debug_set(const char *key, int value) {
     else if (eq("abs")) g_abs_override = value;
     else if (eq("ablate")) g_ablate = value;
     else if (eq("full_sm")) g_full_sm = value;
+    else if (eq("force_per")) g_force_per = value;
+    else if (eq("force_splits")) g_force_splits = value;
     else if (eq("budget_pct")) g_budget_pct = value > 0 ? value : 0;
     else return SAL_E_UNSUPPORTED;
     return SAL_OK;
