@@ -31,6 +31,18 @@ int sal_residual_rmsnorm_f16(const void *x, const void *delta, const void *weigh
 int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos, const void *sin, const int64_t *pos,
                           void *k_cache, void *v_cache, int heads, int kv_heads, int hd, int max_len, void *stream);
 
+/* Variants for products that ran with SAL_OUT_F32_ATOMIC (their outputs are fp32 accumulators).  Every
+ * accumulator element is rounded to fp16 when read — the value the fp16-output path would have stored — and
+ * then set back to zero, so the buffer is ready for the same layer's product of the next token.
+ * sal_residual_rmsnorm_f32acc: as sal_residual_rmsnorm_f16 with delta fp32 (may be NULL); additionally clears
+ * zero_a[0..zero_a_n) and zero_b[0..zero_b_n) (accumulators, e.g. gate and up, whose reader was a GEMV).
+ * sal_rope_kv_write_f32acc: as sal_rope_kv_write_f16 with q, k, v fp32; the rotated query goes to q_out (fp16). */
+int sal_residual_rmsnorm_f32acc(const void *x, void *delta_f32, const void *weight, void *out, void *x_out, int n,
+                                float eps, void *zero_a, int zero_a_n, void *zero_b, int zero_b_n, void *stream);
+int sal_rope_kv_write_f32acc(void *q_f32, void *k_f32, void *v_f32, void *q_out, const void *cos, const void *sin,
+                             const int64_t *pos, void *k_cache, void *v_cache, int heads, int kv_heads, int hd,
+                             int max_len, void *stream);
+
 /* Single-query attention over cache positions 0..*pos: out [heads][hd] fp16.  Grouped-query
  * attention when heads > kv_heads (heads % kv_heads == 0).  hd <= 256, max_len <= 16384. */
 int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,

@@ -54,6 +54,14 @@ extern "C" {
 #define SAL_PDL 2u         /* launch with programmatic dependent launch: the packed planes are
                               prefetched while the previous kernel of the stream drains */
 #define SAL_FORCE_GENERIC 4u /* use the shape-agnostic kernel even where the tiled one applies */
+#define SAL_OUT_F32_ATOMIC 8u /* y is FLOAT32 [N]: bias + product is ADDED to it with fp32 atomic adds (M = 1,
+                                 tiled shapes only).  This is the reference's own output contract — its kernels
+                                 atomicAdd into `output` (mv_fp16_bias.hpp:101) — carried out in fp32.  No
+                                 scratch and no split-K reduction tail, but the summation order is not fixed:
+                                 results can differ in the last fp32 bit from run to run.  The caller zeroes
+                                 (or pre-loads) y. */
+#define SAL_SWIGLU_F32 16u   /* with sal_problem.x_mul: x and x_mul are FLOAT32 (accumulators written with
+                                 SAL_OUT_F32_ATOMIC), rounded to fp16 before silu(x) * x_mul is formed */
 
 #define SAL_MAX_Q 8
 #define SAL_MAX_M 64

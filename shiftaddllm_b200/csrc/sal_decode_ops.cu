@@ -60,6 +60,67 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_kernel(const __half *x,
     }
 }
 
+// fp32-accumulator variant: delta is an fp32 vector written by SAL_OUT_F32_ATOMIC products; it is rounded to
+// fp16 (what the fp16-output path would have stored), consumed, and zeroed for its next use, together with up
+// to two more accumulator vectors whose consumers (many CTAs of a GEMV) could not zero them themselves.
+__global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half *x, float *delta, const __half *w, __half *out,
+                                                                    __half *x_out, int n, float eps, float *zero_a, int zero_a_n,
+                                                                    float *zero_b, int zero_b_n) {
+    __shared__ float red[32];
+    extern __shared__ float tbuf[];  // n floats
+    pdl_prologue();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        float t = __half2float(x[i]);
+        if (delta) {
+            t = __half2float(__float2half_rn(t + __half2float(__float2half_rn(delta[i]))));
+            delta[i] = 0.f;
+        }
+        tbuf[i] = t;
+        ss += t * t;
+    }
+    for (int i = threadIdx.x; i < zero_a_n; i += blockDim.x) zero_a[i] = 0.f;
+    for (int i = threadIdx.x; i < zero_b_n; i += blockDim.x) zero_b[i] = 0.f;
+    ss = block_reduce(ss, red, false);
+    const float inv = rsqrtf(ss / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float t = tbuf[i];
+        if (x_out) x_out[i] = __float2half_rn(t);
+        out[i] = __float2half_rn(t * inv * __half2float(w[i]));
+    }
+}
+
+// fp32-accumulator variant of the rotary step: q, k, v are fp32 accumulators (rounded to fp16 on read, then
+// zeroed); the rotated query goes to q_out (fp16), rotated k and v to the caches.
+__global__ void rope_kv_write_f32_kernel(float *q, float *k, float *v, __half *q_out, const float *cos_t, const float *sin_t,
+                                         const int64_t *pos_p, __half *k_cache, __half *v_cache, int heads, int kv_heads,
+                                         int hd, int max_len) {
+    pdl_prologue();
+    const int64_t pos = *pos_p;
+    if (pos < 0 || pos >= max_len) return;
+    const int half = hd / 2;
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int nq = heads * half, nk = kv_heads * half, nv = kv_heads * hd;
+    if (idx < nq + nk) {
+        const bool is_q = idx < nq;
+        const int j = is_q ? idx : idx - nq;
+        const int h = j / half, i = j % half;
+        const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
+        float *src = is_q ? q : k;
+        const float a = __half2float(__float2half_rn(src[h * hd + i])), b = __half2float(__float2half_rn(src[h * hd + half + i]));
+        src[h * hd + i] = 0.f;
+        src[h * hd + half + i] = 0.f;
+        const __half ra = __float2half_rn(a * c - b * s), rb = __float2half_rn(b * c + a * s);
+        __half *dst = is_q ? q_out : k_cache + ((size_t)pos * kv_heads) * hd;
+        dst[h * hd + i] = ra;
+        dst[h * hd + half + i] = rb;
+    } else if (idx < nq + nk + nv) {
+        const int j = idx - nq - nk;
+        v_cache[(size_t)pos * kv_heads * hd + j] = __float2half_rn(v[j]);
+        v[j] = 0.f;
+    }
+}
+
 // one thread per (head, pair index); q heads first, then k heads, then v copy
 __global__ void rope_kv_write_kernel(__half *q, const __half *k, const __half *v, const float *cos_t, const float *sin_t,
                                      const int64_t *pos_p, __half *k_cache, __half *v_cache, int heads, int kv_heads,
@@ -231,6 +292,29 @@ int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos
     const int total = heads * (hd / 2) + kv_heads * (hd / 2) + kv_heads * hd;
     return launch_pdl(rope_kv_write_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, reinterpret_cast<__half *>(q),
                       reinterpret_cast<const __half *>(k), reinterpret_cast<const __half *>(v),
+                      reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin), pos,
+                      reinterpret_cast<__half *>(k_cache), reinterpret_cast<__half *>(v_cache), heads, kv_heads, hd, max_len);
+}
+
+int sal_residual_rmsnorm_f32acc(const void *x, void *delta_f32, const void *weight, void *out, void *x_out, int n, float eps,
+                                void *zero_a, int zero_a_n, void *zero_b, int zero_b_n, void *stream) {
+    if (!x || !weight || !out) return SAL_E_NULL;
+    if (n < 1 || n > 32768 || zero_a_n < 0 || zero_b_n < 0 || (zero_a_n && !zero_a) || (zero_b_n && !zero_b)) return SAL_E_SHAPE;
+    const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
+    return launch_pdl(residual_rmsnorm_f32_kernel, dim3(1), dim3(threads), (size_t)n * sizeof(float), stream,
+                      reinterpret_cast<const __half *>(x), reinterpret_cast<float *>(delta_f32),
+                      reinterpret_cast<const __half *>(weight), reinterpret_cast<__half *>(out), reinterpret_cast<__half *>(x_out),
+                      n, eps, reinterpret_cast<float *>(zero_a), zero_a_n, reinterpret_cast<float *>(zero_b), zero_b_n);
+}
+
+int sal_rope_kv_write_f32acc(void *q_f32, void *k_f32, void *v_f32, void *q_out, const void *cos, const void *sin,
+                             const int64_t *pos, void *k_cache, void *v_cache, int heads, int kv_heads, int hd, int max_len,
+                             void *stream) {
+    if (!q_f32 || !k_f32 || !v_f32 || !q_out || !cos || !sin || !pos || !k_cache || !v_cache) return SAL_E_NULL;
+    if (heads < 1 || kv_heads < 1 || hd < 2 || (hd & 1) || max_len < 1) return SAL_E_SHAPE;
+    const int total = heads * (hd / 2) + kv_heads * (hd / 2) + kv_heads * hd;
+    return launch_pdl(rope_kv_write_f32_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, reinterpret_cast<float *>(q_f32),
+                      reinterpret_cast<float *>(k_f32), reinterpret_cast<float *>(v_f32), reinterpret_cast<__half *>(q_out),
                       reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin), pos,
                       reinterpret_cast<__half *>(k_cache), reinterpret_cast<__half *>(v_cache), heads, kv_heads, hd, max_len);
 }

@@ -206,13 +206,29 @@ struct TileCfg {
 // entries (entry >> 3 = hg).  Bank of every store = lane.  ROWS = 1: fp32 entries of activation
 // row x0.  ROWS = 2: half2 entries, low half = row x0, high half = row x1 (sums are formed in
 // fp32 and rounded once).
-template <int NCW, int ROWS, bool SWIGLU>
+template <int NCW, int ROWS, int SWIGLU>
 __device__ __forceinline__ void build_tables_impl(const __half *__restrict__ x0, const __half *__restrict__ x1,
                                                   const __half *__restrict__ m0, const __half *__restrict__ m1,
                                                   uint32_t lut_half, int warp, int lane) {
     float xf[ROWS][8];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
+        if (SWIGLU == 2) {
+            // gate and up are the fp32 accumulators two earlier products added into (plain loads: they were
+            // written by atomics of the previous kernels, not constant data)
+            const float4 *gp = reinterpret_cast<const float4 *>(r == 0 ? x0 : x1) + 2 * lane;
+            const float4 *up = reinterpret_cast<const float4 *>(r == 0 ? m0 : m1) + 2 * lane;
+            const float4 g0 = gp[0], g1 = gp[1], u0 = up[0], u1 = up[1];
+            const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float gi = __half2float(__float2half_rn(g[i]));   // the two-step path rounds gate and up to fp16 first
+                const float sg = __half2float(__float2half_rn(gi / (1.f + __expf(-gi))));
+                xf[r][i] = __half2float(__float2half_rn(sg * __half2float(__float2half_rn(u[i]))));
+            }
+            continue;
+        }
         const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(r == 0 ? x0 : x1) + lane);
         const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
 #pragma unroll
@@ -221,7 +237,7 @@ __device__ __forceinline__ void build_tables_impl(const __half *__restrict__ x0,
             xf[r][2 * i] = f.x;
             xf[r][2 * i + 1] = f.y;
         }
-        if (SWIGLU) {
+        if (SWIGLU == 1) {
             // fused SwiGLU: the activation is silu(gate) * up, rounded to fp16 after each step exactly as
             // the separate element-wise kernel (and torch's fp16 ops) would produce it
             const uint4 mraw = __ldg(reinterpret_cast<const uint4 *>(r == 0 ? m0 : m1) + lane);
@@ -308,8 +324,10 @@ constexpr uint32_t SMEM_DYNAMIC_BASE = 1024;
 // rows; the same weight tile serves both rows through half2 table entries.  SWIGLU: the activation
 // is silu(x) * x_mul, formed while the tables are built (a separate instantiation, so that the
 // extra registers of that prologue do not weigh on the ordinary kernel).  EXCH: the fused all-gather
-// epilogue (peer stores + counters), likewise its own instantiation.
-template <int Q, int NCW, bool ABS, int ROWS, bool SWIGLU, bool EXCH>
+// epilogue (peer stores + counters), likewise its own instantiation.  SWIGLU = 2: gate and up are fp32.
+// ATOMIC: y is an fp32 accumulator [N]; every CTA adds its partial sums with fp32 atomics (no scratch,
+// no reduction tail; the summation order is not fixed).
+template <int Q, int NCW, bool ABS, int ROWS, int SWIGLU, bool EXCH, bool ATOMIC>
 __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     lutgemv_tiled_kernel(const __grid_constant__ TileParams P) {
     using C = TileCfg<Q, NCW>;
@@ -460,10 +478,16 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         if (!(P.ablate & 2))
         {
             const size_t ko = (size_t)kb * KB_FEATS;
-            // x_mul row = x_mul + (the same element offset the x row has)
-            const __half *m0 = SWIGLU ? pr.x_mul + (xrow0 - pr.x) + ko : nullptr;
-            const __half *m1 = SWIGLU ? pr.x_mul + (xrow1 - pr.x) + ko : nullptr;
-            build_tables_impl<NCW, ROWS, SWIGLU>(xrow0 + ko, xrow1 + ko, m0, m1, lut_s + PAR * 128, warp, lane);
+            if (SWIGLU == 2) {   // fp32 operands: same element offsets, twice the bytes (pointers are carried as __half*)
+                const __half *g32 = pr.x + 2 * ((xrow0 - pr.x) + ko);
+                const __half *u32 = pr.x_mul + 2 * ((xrow0 - pr.x) + ko);
+                build_tables_impl<NCW, ROWS, SWIGLU>(g32, g32, u32, u32, lut_s + PAR * 128, warp, lane);
+            } else {
+                // x_mul row = x_mul + (the same element offset the x row has)
+                const __half *m0 = SWIGLU ? pr.x_mul + (xrow0 - pr.x) + ko : nullptr;
+                const __half *m1 = SWIGLU ? pr.x_mul + (xrow1 - pr.x) + ko : nullptr;
+                build_tables_impl<NCW, ROWS, SWIGLU>(xrow0 + ko, xrow1 + ko, m0, m1, lut_s + PAR * 128, warp, lane);
+            }
         }
         consumer_barrier(NCW * 32);
         // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
@@ -554,6 +578,20 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     }
 
     // ---------------------------------- epilogue ----------------------------------
+    if (ATOMIC) {
+        // y is an fp32 accumulator: fire-and-forget reductions in L2, nothing to wait for
+        float *yacc = reinterpret_cast<float *>(pr.y);
+#pragma unroll
+        for (int sub = 0; sub < MAX_SUB; ++sub) {
+            const int n = (sub_begin + sub) * CW + col;
+            if (sub < nsub && n < N) {
+                float v = acc[0][sub];
+                if (split == 0 && pr.bias) v += __half2float(pr.bias[n]);
+                atomicAdd(yacc + n, v);
+            }
+        }
+        return;
+    }
     if (pr.splits == 1) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
@@ -959,9 +997,9 @@ int encode_weight_map(CUtensorMap *out, const void *bw, int K, int N, int q) {
     return r == CUDA_SUCCESS ? SAL_OK : SAL_E_LAUNCH;
 }
 
-template <int Q, int NCW, bool ABS, int ROWS, bool SWIGLU, bool EXCH = false>
+template <int Q, int NCW, bool ABS, int ROWS, int SWIGLU, bool EXCH = false, bool ATOMIC = false>
 cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int row_groups, int smem, unsigned flags, cudaStream_t stream) {
-    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS, ROWS, SWIGLU, EXCH>;
+    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS, ROWS, SWIGLU, EXCH, ATOMIC>;
     static int configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -985,24 +1023,31 @@ cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int row_groups, 
     return cudaLaunchKernelEx(&cfg, kern, P);
 }
 
+// swiglu: 0 plain activations, 1 silu(x)*x_mul with fp16 operands, 2 with fp32 operands
 template <int Q, bool ABS>
-cudaError_t launch_tiled_abs(const TileParams &P, int rows, int row_groups, bool swiglu, int ctas, int smem, unsigned flags,
-                             cudaStream_t stream) {
+cudaError_t launch_tiled_abs(const TileParams &P, int rows, int row_groups, int swiglu, bool atomic_out, int ctas, int smem,
+                             unsigned flags, cudaStream_t stream) {
     if (P.ex.world > 1)   // fused exchange: M = 1, plain activations (checked by the caller)
-        return launch_tiled_variant<Q, 8, ABS, 1, false, true>(P, ctas, 1, smem, flags, stream);
+        return launch_tiled_variant<Q, 8, ABS, 1, 0, true>(P, ctas, 1, smem, flags, stream);
     if (rows == 2)
-        return swiglu ? launch_tiled_variant<Q, 8, ABS, 2, true>(P, ctas, row_groups, smem, flags, stream)
-                      : launch_tiled_variant<Q, 8, ABS, 2, false>(P, ctas, row_groups, smem, flags, stream);
-    return swiglu ? launch_tiled_variant<Q, 8, ABS, 1, true>(P, ctas, 1, smem, flags, stream)
-                  : launch_tiled_variant<Q, 8, ABS, 1, false>(P, ctas, 1, smem, flags, stream);
+        return swiglu ? launch_tiled_variant<Q, 8, ABS, 2, 1>(P, ctas, row_groups, smem, flags, stream)
+                      : launch_tiled_variant<Q, 8, ABS, 2, 0>(P, ctas, row_groups, smem, flags, stream);
+    if (atomic_out) {
+        if (swiglu == 2) return launch_tiled_variant<Q, 8, ABS, 1, 2, false, true>(P, ctas, 1, smem, flags, stream);
+        if (swiglu == 1) return launch_tiled_variant<Q, 8, ABS, 1, 1, false, true>(P, ctas, 1, smem, flags, stream);
+        return launch_tiled_variant<Q, 8, ABS, 1, 0, false, true>(P, ctas, 1, smem, flags, stream);
+    }
+    if (swiglu == 2) return launch_tiled_variant<Q, 8, ABS, 1, 2>(P, ctas, 1, smem, flags, stream);
+    return swiglu ? launch_tiled_variant<Q, 8, ABS, 1, 1>(P, ctas, 1, smem, flags, stream)
+                  : launch_tiled_variant<Q, 8, ABS, 1, 0>(P, ctas, 1, smem, flags, stream);
 }
 
 template <int Q>
-cudaError_t launch_tiled(const TileParams &P, int ctas, int rows, int row_groups, bool swiglu, int smem, unsigned flags,
-                         bool abs_ok, cudaStream_t stream) {
+cudaError_t launch_tiled(const TileParams &P, int ctas, int rows, int row_groups, int swiglu, bool atomic_out, int smem,
+                         unsigned flags, bool abs_ok, cudaStream_t stream) {
     const bool use_abs = g_abs_override >= 0 ? (g_abs_override != 0) : abs_ok;
-    return use_abs ? launch_tiled_abs<Q, true>(P, rows, row_groups, swiglu, ctas, smem, flags, stream)
-                   : launch_tiled_abs<Q, false>(P, rows, row_groups, swiglu, ctas, smem, flags, stream);
+    return use_abs ? launch_tiled_abs<Q, true>(P, rows, row_groups, swiglu, atomic_out, ctas, smem, flags, stream)
+                   : launch_tiled_abs<Q, false>(P, rows, row_groups, swiglu, atomic_out, ctas, smem, flags, stream);
 }
 
 bool tiled_eligible(const void *bw, const void *alpha, const void *bias, const void *x, const void *y, int M, int K,
@@ -1072,7 +1117,10 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const int rows = M > 1 ? 2 : 1;
     const int row_groups = (M + rows - 1) / rows;
     const int ncw = 8;   // consumer warps per CTA (a 16-warp, one-CTA-per-SM shape was measured and is not faster)
-    const bool swiglu = problems[0].x_mul != nullptr;   // all problems of a launch must agree
+    // all problems of a launch must agree on the activation form
+    const bool atomic_out = (flags & SAL_OUT_F32_ATOMIC) != 0;
+    const int swiglu = problems[0].x_mul == nullptr ? 0 : ((flags & SAL_SWIGLU_F32) ? 2 : 1);
+    if ((atomic_out || swiglu == 2) && (M != 1 || ex)) return SAL_E_UNSUPPORTED;
     const int cw = ncw * 32;
     const int ctas_per_sm = ncw > 8 ? 1 : 2;
     const int stages = choose_stages(q, ncw, optin, &smem);
@@ -1113,7 +1161,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         const int pct = g_budget_pct > 0 ? g_budget_pct : 100 * ctas_per_sm;
         int budget = (int)(sms * (pct / 100.0) * units / units_total / row_groups + 0.5);  // row groups share the SMs
         if (budget < 4) budget = 4;
-        Plan pl = plan_problem(sp.K, sp.N, budget, have_ws, cw);
+        Plan pl = plan_problem(sp.K, sp.N, budget, have_ws || atomic_out, cw);
         TileProblem &tp = P.p[i];
         tp.bw = reinterpret_cast<const uint32_t *>(sp.bw);
         tp.alpha = reinterpret_cast<const __half *>(sp.alpha);
@@ -1137,7 +1185,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
             const int erc = encode_weight_map(&P.tmap[i], sp.bw, sp.K, sp.N, sp.q);
             if (erc != SAL_OK) return erc;
         }
-        if (pl.splits > 1) {
+        if (pl.splits > 1 && !atomic_out) {
             if (counter_off + pl.ranges * row_groups > WS_MAX_COUNTERS) return SAL_E_WORKSPACE;
             const size_t need = WS_PARTIAL_OFFSET + (n_off + (size_t)sp.N) * (size_t)M * MAX_SPLIT * sizeof(float);
             if (!info_only && need > ws_bytes) return SAL_E_WORKSPACE;
@@ -1176,10 +1224,10 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     const bool abs_ok = dev->smem_base == (int)SMEM_DYNAMIC_BASE;
     cudaError_t e;
     switch (q) {
-        case 1: e = launch_tiled<1>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
-        case 2: e = launch_tiled<2>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
-        case 3: e = launch_tiled<3>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
-        default: e = launch_tiled<4>(P, cta, rows, row_groups, swiglu, smem, flags, abs_ok, stream); break;
+        case 1: e = launch_tiled<1>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
+        case 2: e = launch_tiled<2>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
+        case 3: e = launch_tiled<3>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
+        default: e = launch_tiled<4>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
     }
     return cuda_ok(e) ? SAL_OK : SAL_E_LAUNCH;
 }

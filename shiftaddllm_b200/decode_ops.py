@@ -27,6 +27,24 @@ def rope_kv_write(q, k, v, cos, sin, pos, k_cache, v_cache, heads, kv_heads, hd)
                                          k_cache.shape[0], _stream(q)), "sal_rope_kv_write_f16")
 
 
+def residual_rmsnorm_f32acc(x, delta32, weight, out, x_out, eps: float, zero_a=None, zero_b=None):
+    """As residual_rmsnorm with an fp32 accumulator as delta (consumed and zeroed); zero_a / zero_b:
+    further fp32 accumulators to clear."""
+    lib = _lib.load()
+    _lib.check(lib.sal_residual_rmsnorm_f32acc(x.data_ptr(), None if delta32 is None else delta32.data_ptr(), weight.data_ptr(),
+                                               out.data_ptr(), None if x_out is None else x_out.data_ptr(), x.numel(), float(eps),
+                                               None if zero_a is None else zero_a.data_ptr(), 0 if zero_a is None else zero_a.numel(),
+                                               None if zero_b is None else zero_b.data_ptr(), 0 if zero_b is None else zero_b.numel(),
+                                               _stream(x)), "sal_residual_rmsnorm_f32acc")
+
+
+def rope_kv_write_f32acc(q32, k32, v32, q_out, cos, sin, pos, k_cache, v_cache, heads, kv_heads, hd):
+    lib = _lib.load()
+    _lib.check(lib.sal_rope_kv_write_f32acc(q32.data_ptr(), k32.data_ptr(), v32.data_ptr(), q_out.data_ptr(), cos.data_ptr(),
+                                            sin.data_ptr(), pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), heads,
+                                            kv_heads, hd, k_cache.shape[0], _stream(q_out)), "sal_rope_kv_write_f32acc")
+
+
 def attention_decode(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, scale: float):
     lib = _lib.load()
     _lib.check(lib.sal_attention_decode_f16(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(),

@@ -77,21 +77,24 @@ class _Block:
                 "gate_proj": self.gate_proj, "up_proj": self.up_proj, "down_proj": self.down_proj}
 
 
-def _group(lins, x, outs, pdl=True, x_mul=None):
+def _group(lins, x, outs, pdl=True, x_mul=None, atomic=False, swiglu_f32=False):
     """One grouped LUT-GEMV launch: every layer of `lins` applied to the same activation row
     (`x_mul` given: to silu(x) * x_mul, formed inside the kernel)."""
     probs = [dict(output=o, bWeight=l.binaryWeight, alpha=l.alpha, bias=l.bias, d_input=x, mSize=l.N, kSize=l.K,
                   nb=l.wbit, num_groups=l.alpha.shape[0], d_input_mul=x_mul) for l, o in zip(lins, outs)]
-    lutgemm.lutgemv_grouped(probs, pdl=pdl)
+    lutgemm.lutgemv_grouped(probs, pdl=pdl, atomic_f32=atomic, swiglu_f32=swiglu_f32)
 
 
 class BcqLlamaDecoder:
     """Greedy batch-1 decoder with a static KV cache of `max_len` positions."""
 
     def __init__(self, shape: LlamaShape, wbits: int = 3, group_size: int = 128, max_len: int = 640, device="cuda",
-                 seed: int = 0, fused: bool = True):
+                 seed: int = 0, fused: bool = True, atomic: bool = False):
         self.shape, self.max_len = shape, max_len
         self.fused = fused   # fused CUDA helpers between the GEMVs (False: plain torch ops)
+        # atomic: the GEMVs add into fp32 accumulators with atomics (no split-K reduction tail, summation
+        # order not fixed) and the helpers consume and clear those accumulators; implies fused
+        self.atomic = atomic
         self.device = torch.device(device)
         gen = torch.Generator(device=self.device).manual_seed(1000003 * seed + 5)
         self.embed = (0.02 * torch.randn(shape.vocab, shape.hidden, device=self.device, generator=gen)).half()
@@ -116,6 +119,11 @@ class BcqLlamaDecoder:
         self._down = torch.empty(1, h, **f16)
         self._x, self._hn = torch.empty(1, h, **f16), torch.empty(1, h, **f16)
         self._attn, self._act = torch.empty(1, h, **f16), torch.empty(1, shape.ffn, **f16)
+        if atomic:
+            f32 = dict(dtype=torch.float32, device=self.device)
+            self._q32, self._k32, self._v32 = torch.zeros(1, h, **f32), torch.zeros(1, kvh * hd, **f32), torch.zeros(1, kvh * hd, **f32)
+            self._o32, self._down32 = torch.zeros(1, h, **f32), torch.zeros(1, h, **f32)
+            self._gate32, self._up32 = torch.zeros(1, shape.ffn, **f32), torch.zeros(1, shape.ffn, **f32)
         self.graph = None
 
     # ---- one token ------------------------------------------------------------------------
@@ -130,6 +138,8 @@ class BcqLlamaDecoder:
     def step(self):
         """Consumes `self.token` at position `self.pos`; leaves logits, the greedy next token in
         `self.token` and `self.pos + 1` in `self.pos`.  Graph-capturable (no host sync)."""
+        if self.atomic:
+            return self._step_atomic()
         if self.fused:
             return self._step_fused()
         s = self.shape
@@ -182,6 +192,33 @@ class BcqLlamaDecoder:
             _group((blk.down_proj,), self._gate, (self._down,), x_mul=self._up)   # SiLU(gate)*up formed in the table build
             delta = self._down
         decode_ops.residual_rmsnorm(x, delta, self.final_norm, hn, x, s.eps)
+        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
+        self.token.copy_(self.logits.argmax().view(1))
+        self.pos.add_(1)
+
+    def _step_atomic(self):
+        """The fused step with fp32 atomic accumulation: every GEMV adds into an fp32 buffer that starts at
+        zero, the helper that consumes a buffer rounds it to fp16 and clears it again (gate/up, whose reader
+        is the down projection itself, are cleared by the next residual+RMSNorm)."""
+        s = self.shape
+        hd, kvh = s.head_dim, s.kv_heads
+        scale = 1.0 / math.sqrt(hd)
+        x, hn = self._x, self._hn
+        torch.index_select(self.embed, 0, self.token, out=x)
+        delta = None
+        for li, blk in enumerate(self.blocks):
+            pend = (self._gate32, self._up32) if li > 0 else (None, None)
+            decode_ops.residual_rmsnorm_f32acc(x, delta, blk.input_norm, hn, x, s.eps, *pend)
+            _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q32, self._k32, self._v32), atomic=True)
+            decode_ops.rope_kv_write_f32acc(self._q32, self._k32, self._v32, self._q, self.cos, self.sin, self.pos,
+                                            self.k_cache[li], self.v_cache[li], s.heads, kvh, hd)
+            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale)
+            _group((blk.o_proj,), self._attn, (self._o32,), atomic=True)
+            decode_ops.residual_rmsnorm_f32acc(x, self._o32, blk.post_norm, hn, x, s.eps)
+            _group((blk.gate_proj, blk.up_proj), hn, (self._gate32, self._up32), atomic=True)
+            _group((blk.down_proj,), self._gate32, (self._down32,), x_mul=self._up32, atomic=True, swiglu_f32=True)
+            delta = self._down32
+        decode_ops.residual_rmsnorm_f32acc(x, delta, self.final_norm, hn, x, s.eps, self._gate32, self._up32)
         self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
         self.token.copy_(self.logits.argmax().view(1))
         self.pos.add_(1)
@@ -270,11 +307,13 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--no-fused", action="store_true", help="plain torch ops between the GEMVs")
+    ap.add_argument("--atomic", action="store_true", help="GEMVs accumulate into fp32 buffers with atomics (no split-K tail)")
     args = ap.parse_args()
     shape = SHAPES[args.model]
-    model = BcqLlamaDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16, fused=not args.no_fused)
+    model = BcqLlamaDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16, fused=not args.no_fused,
+                            atomic=args.atomic)
     res = benchmark(model, args.prompt, args.new)
-    res.update({"fused_helpers": not args.no_fused, "model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompt"})
+    res.update({"atomic_f32_outputs": args.atomic, "fused_helpers": not args.no_fused, "model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompt"})
     print(json.dumps(res))
 
 

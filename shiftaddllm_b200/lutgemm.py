@@ -132,28 +132,36 @@ def lutgemv_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb, num_g
             flags=flags, bias=bias, alpha_numel=int(num_groups) * int(nb) * int(mSize))
 
 
-def lutgemv_grouped(problems, *, pdl=False, accumulate=False):
+def lutgemv_grouped(problems, *, pdl=False, accumulate=False, atomic_f32=False, swiglu_f32=False):
     """Several independent mode-A products in one launch.  ``problems`` is a list
     of dicts with keys output, bWeight, alpha, bias (or None), d_input,
     mSize, kSize, nb, num_groups and optionally d_input_mul (the activation is then
-    silu(d_input) * d_input_mul, computed while the tables are built)."""
+    silu(d_input) * d_input_mul, computed while the tables are built).
+
+    ``atomic_f32=True``: every ``output`` is a float32 accumulator the product is ADDED to with fp32
+    atomics (no split-K reduction tail; summation order not fixed).  ``swiglu_f32=True``: d_input and
+    d_input_mul are such float32 accumulators."""
     lib = _lib.load()
     if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
         raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
     arr = (_lib.SalProblem * len(problems))()
     dev = problems[0]["output"].device
     n_total = 0
+    m_max = 1
+    out_dtype = torch.float32 if atomic_f32 else torch.float16
+    in_dtype = torch.float32 if swiglu_f32 else torch.float16
     for i, p in enumerate(problems):
-        _req(p["output"], torch.float16, "output")
+        _req(p["output"], out_dtype, "output")
         _req(p["bWeight"], torch.int32, "bWeight")
         _req(p["alpha"], torch.float16, "alpha")
-        _req(p["d_input"], torch.float16, "d_input")
+        _req(p["d_input"], in_dtype, "d_input")
         n, k = int(p["mSize"]), int(p["kSize"])
         m = _rows(p["output"], p["d_input"], n, k)
+        m_max = max(m_max, m)
         bias = p.get("bias")
         mul = p.get("d_input_mul")      # optional: the activation is silu(d_input) * d_input_mul
         if mul is not None:
-            _req(mul, torch.float16, "d_input_mul")
+            _req(mul, in_dtype, "d_input_mul")
             if mul.numel() != p["d_input"].numel():
                 raise RuntimeError("d_input_mul must have the shape of d_input")
         arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
@@ -161,9 +169,10 @@ def lutgemv_grouped(problems, *, pdl=False, accumulate=False):
                                  p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]),
                                  mul.data_ptr() if mul is not None else None)
         n_total += n
-    flags = (_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
+    flags = ((_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
+             | (_lib.SAL_OUT_F32_ATOMIC if atomic_f32 else 0) | (_lib.SAL_SWIGLU_F32 if swiglu_f32 else 0))
     with torch.cuda.device(dev):
-        ws = workspace_for(dev, 1, n_total)
+        ws = workspace_for(dev, m_max, n_total)
         stream = torch.cuda.current_stream(dev).cuda_stream
         _lib.check(lib.sal_lutgemv_grouped(arr, len(problems), flags, ws.data_ptr(), ws.numel(), stream),
                    "sal_lutgemv_grouped")

@@ -108,9 +108,10 @@ def test_fused_helpers_match_torch():
     assert float((out.float() - ref).abs().max()) < 4e-3
 
 
-@pytest.mark.parametrize("fused", [False, True])
-def test_tiny_decoder_matches_fp32_reference(fused):
-    model = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, group_size=128, max_len=32, seed=1, fused=fused)
+@pytest.mark.parametrize("mode", ["torch", "fused", "atomic"])
+def test_tiny_decoder_matches_fp32_reference(mode):
+    model = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, group_size=128, max_len=32, seed=1, fused=(mode != "torch"),
+                            atomic=(mode == "atomic"))
     tokens = [5, 17, 999, 3, 42, 7]
     model.reset()
     for i, t in enumerate(tokens):
@@ -135,6 +136,25 @@ def test_graph_replay_equals_eager():
     model.feed(prompt)
     replayed = model.generate(8).cpu()
     assert torch.equal(eager, replayed)            # deterministic kernels: identical greedy tokens
+
+
+def test_atomic_mode_tracks_the_deterministic_mode():
+    """fp32-atomic accumulation only changes the summation order: greedy tokens over a short
+    generation agree with the deterministic path, and the accumulators are left clean."""
+    a = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=64, seed=4, fused=True)
+    b = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=64, seed=4, fused=True, atomic=True)
+    for m in (a, b):
+        m.reset()
+        m.feed([3, 1, 4, 1, 5])
+    ta, tb = a.generate(6).cpu(), b.generate(6).cpu()
+    assert torch.equal(ta, tb)
+    torch.cuda.synchronize()
+    for buf in (b._q32, b._k32, b._v32, b._o32, b._gate32, b._up32):
+        assert float(buf.abs().max()) == 0.0          # consumed and cleared (down32 is cleared by the next step)
+    b.capture()
+    b.reset()
+    b.feed([3, 1, 4, 1, 5])
+    assert torch.equal(b.generate(6).cpu(), ta)
 
 
 def test_benchmark_runs():
