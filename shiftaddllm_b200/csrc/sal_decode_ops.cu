@@ -299,7 +299,7 @@ int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos
 int sal_residual_rmsnorm_f32acc(const void *x, void *delta_f32, const void *weight, void *out, void *x_out, int n, float eps,
                                 void *zero_a, int zero_a_n, void *zero_b, int zero_b_n, void *stream) {
     if (!x || !weight || !out) return SAL_E_NULL;
-    if (n < 1 || n > 32768 || zero_a_n < 0 || zero_b_n < 0 || (zero_a_n && !zero_a) || (zero_b_n && !zero_b)) return SAL_E_SHAPE;
+    if (n < 1 || n > 12288 /* the row is staged in 48 KB of shared memory */ || zero_a_n < 0 || zero_b_n < 0 || (zero_a_n && !zero_a) || (zero_b_n && !zero_b)) return SAL_E_SHAPE;
     const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
     return launch_pdl(residual_rmsnorm_f32_kernel, dim3(1), dim3(threads), (size_t)n * sizeof(float), stream,
                       reinterpret_cast<const __half *>(x), reinterpret_cast<float *>(delta_f32),

@@ -57,6 +57,8 @@ constexpr int WS_MAX_COUNTERS = WS_COUNTER_BYTES / 4;
 constexpr size_t WS_PARTIAL_OFFSET = 16384;
 constexpr int BOX_COLS = 256;             // columns of one TMA box (the limit of a tensor-map box dimension)
 
+enum AlphaKind { A_ROW_F16 = 0, A_ROW_HALVING = 1, B_F16 = 2, B_U16 = 3, B_I8 = 4 };
+
 struct TileProblem {
     const uint32_t *bw;
     const __half *alpha;
@@ -73,6 +75,11 @@ struct TileProblem {
     int nsub_per_range;
     int ranges, splits;
     int cta_begin;
+    // block mode (one multiplier per 8 input features x `blk_gs` output columns, alpha [K/8][q][N/blk_gs]):
+    int blk_kind;     // 0 = off (alpha per K group and column), else the AlphaKind of the multipliers
+    int blk_gs;       // columns per group: 16, 32, 64, 128 or a multiple of 256
+    int blk_ngroups;  // N / blk_gs
+    int blk_apot;     // int8 encoding: exponents per multiplier (<= 4)
     long long gather_off;  // fused exchange: element offset of this problem's [world][N] block in the peer buffers
 };
 
@@ -327,9 +334,15 @@ constexpr uint32_t SMEM_DYNAMIC_BASE = 1024;
 // epilogue (peer stores + counters), likewise its own instantiation.  SWIGLU = 2: gate and up are fp32.
 // ATOMIC: y is an fp32 accumulator [N]; every CTA adds its partial sums with fp32 atomics (no scratch,
 // no reduction tail; the summation order is not fixed).
-template <int Q, int NCW, bool ABS, int ROWS, int SWIGLU, bool EXCH, bool ATOMIC>
+// BLK: block mode.  Every lookup has its own multiplier alpha[chunk][plane][column / gs].  The multipliers
+// of a tile (32 chunks x Q planes x up to 16 column groups) are fetched one tile ahead, decoded to fp32
+// and parked in the upper 128 bytes of the table rows (this mode keeps ONE set of tables, in the lower
+// halves): row (buffer * Q + plane) * 16 + group, chunk c of group gi at byte 128 + 4 * (c ^ gi), which
+// makes both the decode stores and the skewed reads conflict-free.  ROWS = 1, blockIdx.y = activation row.
+template <int Q, int NCW, bool ABS, int ROWS, int SWIGLU, bool EXCH, bool ATOMIC, bool BLK>
 __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     lutgemv_tiled_kernel(const __grid_constant__ TileParams P) {
+    static_assert(!BLK || (ROWS == 1 && SWIGLU == 0 && !EXCH && !ATOMIC && Q <= 8), "block mode: plain M-row kernel only");
     using C = TileCfg<Q, NCW>;
     constexpr int CW = C::CW;
     extern __shared__ __align__(128) unsigned char smem[];
@@ -435,6 +448,22 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             for (int t = 0; t < 4; ++t) pk |= (unsigned)(16 * wi + 4 * ((t + s4) & 3)) << (8 * t);
             cpack[hp][j] = pk;
         }
+    // block mode: the same chunk offsets with the lane's group folded in, and the row of the lane's group
+    unsigned mpack[BLK ? 2 : 1][BLK ? 4 : 1];
+    uint32_t mrow = 0;
+    int blk_gt = 1, blk_gshift = 0;  // column groups per tile and its log2
+    if constexpr (BLK) {
+        if (pr.blk_gs < BOX_COLS) {
+            blk_gt = BOX_COLS / pr.blk_gs;
+            blk_gshift = 31 - __clz(blk_gt);
+        }
+        const unsigned grp = pr.blk_gs < BOX_COLS ? (unsigned)(col / pr.blk_gs) : 0u;
+        mrow = grp * (unsigned)LUT_ROW_BYTES;
+#pragma unroll
+        for (int hp = 0; hp < 2; ++hp)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) mpack[hp][j] = cpack[hp][j] ^ (0x01010101u * (4u * grp));
+    }
 
     float acc[ROWS][MAX_SUB];
 #pragma unroll
@@ -460,11 +489,107 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         }
     };
     __half a_next[2][Q];
-    if (kb_begin < kb_end && !(P.ablate & 1)) load_alpha(kb_begin, 0, a_next);  // constants: legal before the dependency wait
+    if (!BLK && kb_begin < kb_end && !(P.ablate & 1)) load_alpha(kb_begin, 0, a_next);  // constants: legal before the dependency wait
     else {
 #pragma unroll
         for (int b = 0; b < Q; ++b) a_next[0][b] = a_next[1][b] = __float2half(0.f);
     }
+    // block mode, multipliers of one tile (32 chunks x Q planes x `blk_gt` column groups), fetched by the
+    // 256 consumer threads.  16/8/4 groups per tile: item e = tid + 256 i is FOUR consecutive groups
+    // (one 8- or 12-byte run of alpha) of one (chunk, plane); 1 or 2 groups per tile: item = one value.
+    // The chunk bits of an item are arranged so that the 32 stores of a warp hit 32 different banks.
+    constexpr int NVI = BLK ? (Q + 1) / 2 : 1;   // items per thread
+    constexpr int NVW = BLK ? 3 : 1;             // 32-bit words per item (12 bytes of int8 x 3, 8 bytes of 16-bit)
+    uint32_t raw_next[NVI][NVW];
+    const bool blk_quads = blk_gt >= 4;
+    auto item_coords = [&](int e, int &gi, int &c, int &b) {
+        if (blk_quads) {
+            const int qmask = (blk_gt >> 2) - 1, cb = e >> (blk_gshift - 2);
+            gi = (e & qmask) << 2;
+            c = (cb & 3) | (((cb >> 3) & 3) << 2) | (((cb >> 2) & 1) << 4);
+            b = cb >> 5;
+        } else {
+            const int idx = e >> blk_gshift;
+            gi = e & (blk_gt - 1);
+            c = ((idx & 1) << 4) | ((idx >> 1) & 15);
+            b = idx >> 5;
+        }
+    };
+    auto load_block_alpha = [&](int kb, int sub, uint32_t(&dst)[NVI][NVW]) {
+        const int g0 = ((sub_begin + sub) * CW) / pr.blk_gs;
+#pragma unroll
+        for (int i = 0; i < NVI; ++i) {
+            int gi, c, b;
+            item_coords(tid + 256 * i, gi, c, b);
+            dst[i][0] = dst[i][1] = dst[i][2] = 0u;
+            if (b < Q) {
+                // groups past the last one belong to columns past N, whose results are never stored
+                const int gq = min(g0 + gi, pr.blk_ngroups - (blk_quads ? 4 : 1));
+                const size_t a = ((size_t)(kb * 32 + c) * Q + b) * pr.blk_ngroups + gq;
+                if (blk_quads) {
+                    if (pr.blk_kind == B_I8) {
+                        const uint32_t *ap = reinterpret_cast<const uint32_t *>(reinterpret_cast<const uint8_t *>(pr.alpha) + a * 3);
+                        dst[i][0] = __ldg(ap);
+                        dst[i][1] = __ldg(ap + 1);
+                        dst[i][2] = __ldg(ap + 2);
+                    } else {
+                        const uint2 v = __ldg(reinterpret_cast<const uint2 *>(reinterpret_cast<const uint16_t *>(pr.alpha) + a));
+                        dst[i][0] = v.x;
+                        dst[i][1] = v.y;
+                    }
+                } else if (pr.blk_kind == B_I8) {
+                    const uint8_t *ap = reinterpret_cast<const uint8_t *>(pr.alpha) + a * 3;
+                    dst[i][0] = (uint32_t)__ldg(ap) | ((uint32_t)__ldg(ap + 1) << 8) | ((uint32_t)__ldg(ap + 2) << 16);
+                } else {
+                    dst[i][0] = __ldg(reinterpret_cast<const uint16_t *>(pr.alpha) + a);
+                }
+            }
+        }
+    };
+    auto decode_mult = [&](uint32_t v) -> float {   // v: 16 bits (fp16 / three 3-bit exponents) or three int8 exponents
+        if (pr.blk_kind == B_F16) return __half2float(__ushort_as_half((unsigned short)v));
+        if (pr.blk_kind == B_U16) return (float)(1u << (v & 7u)) + (float)(1u << ((v >> 3) & 7u)) + (float)(1u << ((v >> 6) & 7u));
+        float m = 0.f;
+#pragma unroll
+        for (int t = 0; t < 3; ++t) {
+            const int sft = (int)(int8_t)(v >> (8 * t));
+            if (sft != -128) m += exp2f((float)sft);
+        }
+        return m;
+    };
+    auto store_block_mult = [&](const uint32_t(&src)[NVI][NVW], uint32_t buffer_off) {
+#pragma unroll
+        for (int i = 0; i < NVI; ++i) {
+            int gi, c, b;
+            item_coords(tid + 256 * i, gi, c, b);
+            if (b < Q) {
+                const uint32_t row0 = lut_s + buffer_off + (uint32_t)((b * 16 + gi) * LUT_ROW_BYTES + 128);
+                if (blk_quads) {
+                    uint32_t v[4];
+                    if (pr.blk_kind == B_I8) {
+                        v[0] = src[i][0];
+                        v[1] = (src[i][0] >> 24) | (src[i][1] << 8);
+                        v[2] = (src[i][1] >> 16) | (src[i][2] << 16);
+                        v[3] = src[i][2] >> 8;
+                    } else {
+                        v[0] = src[i][0] & 0xFFFFu;
+                        v[1] = src[i][0] >> 16;
+                        v[2] = src[i][1] & 0xFFFFu;
+                        v[3] = src[i][1] >> 16;
+                    }
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        sts_f32(row0 + (uint32_t)(k * LUT_ROW_BYTES + 4 * (c ^ (gi + k))), decode_mult(v[k]));
+                } else {
+                    sts_f32(row0 + (uint32_t)(4 * (c ^ gi)), decode_mult(src[i][0]));
+                }
+            }
+        }
+    };
+    if constexpr (BLK) {
+        if (kb_begin < kb_end) load_block_alpha(kb_begin, 0, raw_next);
+    }
+    uint32_t mbuf = 0;  // byte offset of the multiplier buffer the current tile uses (two buffers, alternating)
 
     pdl_wait();  // activations, bias, y and the scratch buffer may be written by the previous kernel
 
@@ -474,7 +599,8 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     uint32_t phase = 0;
     // One K block: build its tables into half `PAR` of the table rows, then walk the column tiles.
     auto process_block = [&](int kb, auto par_tag) {
-        constexpr int PAR = decltype(par_tag)::value;
+        constexpr int PAR = BLK ? 0 : decltype(par_tag)::value;
+        if constexpr (BLK) consumer_barrier(NCW * 32);  // one set of tables: the previous K block must be finished by all
         if (!(P.ablate & 2))
         {
             const size_t ko = (size_t)kb * KB_FEATS;
@@ -503,7 +629,20 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             {
                 const bool more_sub = (sub + 1 < nsub);
                 const int kb_n = more_sub ? kb : kb + 1;
-                if (kb_n < kb_end && !(P.ablate & 1)) load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
+                if constexpr (BLK) {
+                    uint32_t raw_cur[NVI][NVW];
+#pragma unroll
+                    for (int i = 0; i < NVI; ++i)
+#pragma unroll
+                        for (int k = 0; k < NVW; ++k) raw_cur[i][k] = raw_next[i][k];
+                    if (kb_n < kb_end && !(P.ablate & 1)) load_block_alpha(kb_n, more_sub ? sub + 1 : 0, raw_next);
+                    // Safe without a second barrier: whoever writes buffer `mbuf` again has passed the barrier of
+                    // the tile in between, which every warp reaches only after its reads of this tile.
+                    if (!(P.ablate & 8)) store_block_mult(raw_cur, mbuf);
+                    if (!(P.ablate & 16)) consumer_barrier(NCW * 32);
+                } else if (kb_n < kb_end && !(P.ablate & 1)) {
+                    load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
+                }
             }
             mbar_wait(full0 + 8 * st, phase, P.status);
             const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
@@ -518,13 +657,39 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                 for (int r = 0; r < ROWS; ++r)
 #pragma unroll
                     for (int b = 0; b < Q; ++b) part[r][b] = part2[r][b] = 0.f;
+                // block mode: all weight words of this half are requested before the first lookup, so that the
+                // (longer) chains table load -> multiplier load -> fma of one word overlap the next word's load
+                uint32_t wpre[BLK ? 4 : 1][BLK ? Q : 1];
+                if constexpr (BLK) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint32_t wr = wrow[hp][j] + soff;
+#pragma unroll
+                        for (int b = 0; b < Q; ++b) {
+                            if (b == 0) wpre[j][b] = lds_u32_imm<0>(wr);
+                            else if (b == 1) wpre[j][b] = lds_u32_imm<1 * BOX_COLS * 4>(wr);
+                            else if (b == 2) wpre[j][b] = lds_u32_imm<2 * BOX_COLS * 4>(wr);
+                            else wpre[j][b] = lds_u32_imm<3 * BOX_COLS * 4>(wr);
+                        }
+                    }
+                }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const uint32_t wr = wrow[hp][j] + soff;
+                    uint32_t ma[4] = {0u, 0u, 0u, 0u};
+                    if constexpr (BLK) {
+                        // multiplier address: byte 0 <- 4 * (chunk ^ group), bytes 1.. <- row of (buffer, group)
+                        const uint32_t rowsel = mrow + mbuf;
+                        ma[0] = prmt(mpack[hp][j], rowsel, 0x7650u) + (ABS ? 0u : lut_s);
+                        ma[1] = prmt(mpack[hp][j], rowsel, 0x7651u) + (ABS ? 0u : lut_s);
+                        ma[2] = prmt(mpack[hp][j], rowsel, 0x7652u) + (ABS ? 0u : lut_s);
+                        ma[3] = prmt(mpack[hp][j], rowsel, 0x7653u) + (ABS ? 0u : lut_s);
+                    }
 #pragma unroll
                     for (int b = 0; b < Q; ++b) {
                         uint32_t w;
-                        if (b == 0) w = lds_u32_imm<0>(wr);
+                        if constexpr (BLK) w = wpre[j][b];
+                        else if (b == 0) w = lds_u32_imm<0>(wr);
                         else if (b == 1) w = lds_u32_imm<1 * BOX_COLS * 4>(wr);
                         else if (b == 2) w = lds_u32_imm<2 * BOX_COLS * 4>(wr);
                         else w = lds_u32_imm<3 * BOX_COLS * 4>(wr);
@@ -534,7 +699,21 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                             const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
                             e[t] = ABS ? lds_u32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off) : lds_u32_imm<0>(off + lut_s + PAR * 128);
                         }
-                        if (ROWS == 1) {
+                        if constexpr (BLK) {
+                            constexpr int MB = (ABS ? (int)SMEM_DYNAMIC_BASE : 0) + 128;
+                            float m[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                if (b == 0) m[t] = lds_f32_imm<MB>(ma[t]);
+                                else if (b == 1) m[t] = lds_f32_imm<MB + 1 * 16 * LUT_ROW_BYTES>(ma[t]);
+                                else if (b == 2) m[t] = lds_f32_imm<MB + 2 * 16 * LUT_ROW_BYTES>(ma[t]);
+                                else m[t] = lds_f32_imm<MB + 3 * 16 * LUT_ROW_BYTES>(ma[t]);
+                            }
+                            part[0][0] = fmaf(m[0], __uint_as_float(e[0]), part[0][0]);
+                            part2[0][0] = fmaf(m[1], __uint_as_float(e[1]), part2[0][0]);
+                            part[0][0] = fmaf(m[2], __uint_as_float(e[2]), part[0][0]);
+                            part2[0][0] = fmaf(m[3], __uint_as_float(e[3]), part2[0][0]);
+                        } else if (ROWS == 1) {
                             part[0][b] += __uint_as_float(e[0]);
                             part2[0][b] += __uint_as_float(e[1]);
                             part[0][b] += __uint_as_float(e[2]);
@@ -555,11 +734,15 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                         }
                     }
                 }
+                if constexpr (BLK) {
+                    a_sub[0] += part[0][0] + part2[0][0];  // the multipliers are already in
+                } else {
 #pragma unroll
-                for (int b = 0; b < Q; ++b) {
-                    const float a = __half2float((hp ^ hw) ? a_cur[1][b] : a_cur[0][b]);  // slot hp holds group hp ^ hw
+                    for (int b = 0; b < Q; ++b) {
+                        const float a = __half2float((hp ^ hw) ? a_cur[1][b] : a_cur[0][b]);  // slot hp holds group hp ^ hw
 #pragma unroll
-                    for (int r = 0; r < ROWS; ++r) a_sub[r] += a * (part[r][b] + part2[r][b]);
+                        for (int r = 0; r < ROWS; ++r) a_sub[r] += a * (part[r][b] + part2[r][b]);
+                    }
                 }
             }
 #pragma unroll
@@ -570,6 +753,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                 st = 0;
                 phase ^= 1u;
             }
+            if constexpr (BLK) mbuf ^= (uint32_t)(Q * 16 * LUT_ROW_BYTES);
         }
     };
     for (int kb = kb_begin; kb < kb_end; kb += 2) {
@@ -701,8 +885,6 @@ __global__ void smem_base_probe_kernel(uint32_t *out) {
 // ------------------------------------------------------------------------------------------
 // generic kernel: any K % 32 == 0, any N, 1 <= M <= 64, all five alpha encodings
 // ------------------------------------------------------------------------------------------
-enum AlphaKind { A_ROW_F16 = 0, A_ROW_HALVING = 1, B_F16 = 2, B_U16 = 3, B_I8 = 4 };
-
 struct GenericParams {
     const uint32_t *bw;
     const void *alpha;
@@ -997,9 +1179,9 @@ int encode_weight_map(CUtensorMap *out, const void *bw, int K, int N, int q) {
     return r == CUDA_SUCCESS ? SAL_OK : SAL_E_LAUNCH;
 }
 
-template <int Q, int NCW, bool ABS, int ROWS, int SWIGLU, bool EXCH = false, bool ATOMIC = false>
+template <int Q, int NCW, bool ABS, int ROWS, int SWIGLU, bool EXCH = false, bool ATOMIC = false, bool BLK = false>
 cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int row_groups, int smem, unsigned flags, cudaStream_t stream) {
-    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS, ROWS, SWIGLU, EXCH, ATOMIC>;
+    auto kern = lutgemv_tiled_kernel<Q, NCW, ABS, ROWS, SWIGLU, EXCH, ATOMIC, BLK>;
     static int configured[64];
     int dev = 0;
     cudaGetDevice(&dev);
@@ -1027,6 +1209,8 @@ cudaError_t launch_tiled_variant(const TileParams &P, int ctas, int row_groups, 
 template <int Q, bool ABS>
 cudaError_t launch_tiled_abs(const TileParams &P, int rows, int row_groups, int swiglu, bool atomic_out, int ctas, int smem,
                              unsigned flags, cudaStream_t stream) {
+    if (P.p[0].blk_kind)  // block mode: one activation row per grid.y
+        return launch_tiled_variant<Q, 8, ABS, 1, 0, false, false, true>(P, ctas, row_groups, smem, flags, stream);
     if (P.ex.world > 1)   // fused exchange: M = 1, plain activations (checked by the caller)
         return launch_tiled_variant<Q, 8, ABS, 1, 0, true>(P, ctas, 1, smem, flags, stream);
     if (rows == 2)
@@ -1100,8 +1284,28 @@ int run_generic(int kind, GenericParams p, void *workspace, size_t ws_bytes, cud
     return cuda_ok(cudaGetLastError()) ? SAL_OK : SAL_E_LAUNCH;
 }
 
+// Block mode (alpha [K/8][q][N/gs]) of a problem handed to run_tiled_group.
+struct BlockAlpha {
+    int kind;  // B_F16, B_U16 or B_I8
+    int ngroups, gs, num_apot;
+};
+
+bool block_tiled_eligible(const void *bw, const void *alpha, const void *x, int M, int K, int N, int q, int num_groups, int kind,
+                          int num_apot) {
+    if (M < 1 || M > SAL_MAX_M || q < 1 || q > 4) return false;
+    if (K % KB_FEATS != 0 || N % 8 != 0 || N < 8) return false;
+    if (num_groups <= 0 || N % num_groups != 0) return false;
+    const int gs = N / num_groups;
+    if (!(gs == 16 || gs == 32 || gs == 64 || gs == 128 || gs % BOX_COLS == 0)) return false;
+    if (kind == B_I8 && num_apot != 3) return false;  // three exponents per multiplier, as the reference's LutLinear stores them
+    // 16/32/64 columns per group: the kernel fetches four consecutive groups with one aligned 8- or 12-byte load
+    if (gs < 128 && (num_groups % 4 != 0 || !aligned(alpha, 8))) return false;
+    return aligned(bw, 16) && aligned(x, 16) && aligned(alpha, 2);
+}
+
 int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void *workspace, size_t ws_bytes,
-                    cudaStream_t stream, sal_plan_info *info_only, const sal_exchange *ex = nullptr, int *writers_out = nullptr) {
+                    cudaStream_t stream, sal_plan_info *info_only, const sal_exchange *ex = nullptr, int *writers_out = nullptr,
+                    const BlockAlpha *blk = nullptr) {
     DeviceInfo *dev = nullptr;
     if (!info_only) {
         int rc = device_info(&dev);
@@ -1114,13 +1318,14 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     // Activation rows: M = 1 runs the fp32-table kernel; 2 <= M <= 64 runs the half2-table variant,
     // one pair of rows per grid.y (all problems of a launch must agree on M).
     const int M = problems[0].M;
-    const int rows = M > 1 ? 2 : 1;
+    const int rows = (M > 1 && !blk) ? 2 : 1;
     const int row_groups = (M + rows - 1) / rows;
     const int ncw = 8;   // consumer warps per CTA (a 16-warp, one-CTA-per-SM shape was measured and is not faster)
     // all problems of a launch must agree on the activation form
     const bool atomic_out = (flags & SAL_OUT_F32_ATOMIC) != 0;
     const int swiglu = problems[0].x_mul == nullptr ? 0 : ((flags & SAL_SWIGLU_F32) ? 2 : 1);
     if ((atomic_out || swiglu == 2) && (M != 1 || ex)) return SAL_E_UNSUPPORTED;
+    if (blk && (atomic_out || swiglu || ex || count != 1)) return SAL_E_UNSUPPORTED;
     const int cw = ncw * 32;
     const int ctas_per_sm = ncw > 8 ? 1 : 2;
     const int stages = choose_stages(q, ncw, optin, &smem);
@@ -1172,7 +1377,13 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         tp.K = sp.K;
         tp.N = sp.N;
         tp.M = sp.M;
-        tp.g = sp.K / sp.num_groups;
+        tp.g = blk ? KB_FEATS : sp.K / sp.num_groups;
+        if (blk) {
+            tp.blk_kind = blk->kind;
+            tp.blk_gs = blk->gs;
+            tp.blk_ngroups = blk->ngroups;
+            tp.blk_apot = blk->num_apot;
+        }
         tp.kblocks = pl.kblocks;
         tp.nsub_total = pl.nsub_total;
         tp.nsub_per_range = pl.nsub_per_range;
@@ -1393,6 +1604,12 @@ static int block_entry(int kind, const void *bw, const void *alpha, const void *
     p.gs = N / num_groups;
     p.num_apot = num_apot;
     p.accumulate = (flags & SAL_ACCUMULATE) ? 1 : 0;
+    if (!(flags & SAL_FORCE_GENERIC) && block_tiled_eligible(bw, alpha, x, M, K, N, q, num_groups, kind, num_apot)) {
+        sal_problem sp = {bw, alpha, bias, x, y, M, K, N, q, /*num_groups (unused in block mode)*/ 1};
+        const BlockAlpha blk = {kind, num_groups, N / num_groups, num_apot};
+        return run_tiled_group(&sp, 1, flags & (SAL_ACCUMULATE | SAL_PDL), workspace, workspace_bytes,
+                               reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr, &blk);
+    }
     return run_generic(kind, p, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
 

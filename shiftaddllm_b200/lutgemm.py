@@ -132,6 +132,71 @@ def lutgemv_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb, num_g
             flags=flags, bias=bias, alpha_numel=int(num_groups) * int(nb) * int(mSize))
 
 
+class GroupedLaunch:
+    """A grouped launch whose argument block was validated and marshalled once
+    (``prepare_grouped``); calling it enqueues the launch on the current stream
+    of the tensors' device.  The tensors named at preparation are referenced,
+    not copied: their storage must stay where it is."""
+
+    def __init__(self, problems, *, pdl=False, accumulate=False, atomic_f32=False, swiglu_f32=False):
+        self._lib = _lib.load()
+        if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
+            raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
+        self._arr = (_lib.SalProblem * len(problems))()
+        self._count = len(problems)
+        self._device = problems[0]["output"].device
+        self._keep = []          # keeps the tensors (and with them the addresses in _arr) alive
+        self._n_total = 0
+        self._m_max = 1
+        out_dtype = torch.float32 if atomic_f32 else torch.float16
+        in_dtype = torch.float32 if swiglu_f32 else torch.float16
+        for i, p in enumerate(problems):
+            _req(p["output"], out_dtype, "output")
+            _req(p["bWeight"], torch.int32, "bWeight")
+            _req(p["alpha"], torch.float16, "alpha")
+            _req(p["d_input"], in_dtype, "d_input")
+            n, k = int(p["mSize"]), int(p["kSize"])
+            m = _rows(p["output"], p["d_input"], n, k)
+            self._m_max = max(self._m_max, m)
+            bias = p.get("bias")
+            mul = p.get("d_input_mul")      # optional: the activation is silu(d_input) * d_input_mul
+            if mul is not None:
+                _req(mul, in_dtype, "d_input_mul")
+                if mul.numel() != p["d_input"].numel():
+                    raise RuntimeError("d_input_mul must have the shape of d_input")
+            self._arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
+                                           bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
+                                           p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]),
+                                           mul.data_ptr() if mul is not None else None)
+            self._keep.append((p["output"], p["bWeight"], p["alpha"], bias, p["d_input"], mul))
+            self._n_total += n
+        self._flags = ((_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
+                       | (_lib.SAL_OUT_F32_ATOMIC if atomic_f32 else 0) | (_lib.SAL_SWIGLU_F32 if swiglu_f32 else 0))
+        self._fn = self._lib.sal_lutgemv_grouped
+        self._need = self._lib.sal_workspace_bytes(self._m_max, self._n_total)
+        if self._device.index is None:
+            self._device = torch.device("cuda", torch.cuda.current_device())
+
+    def __call__(self):
+        dev = self._device
+        if torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):
+                return self()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        ws = _workspaces.get((dev.index, stream))
+        if ws is None or ws.numel() < self._need:
+            ws = workspace_for(dev, self._m_max, self._n_total)
+        rc = self._fn(self._arr, self._count, self._flags, ws.data_ptr(), ws.numel(), stream)
+        if rc != 0:
+            _lib.check(rc, "sal_lutgemv_grouped")
+
+
+def prepare_grouped(problems, **kwargs) -> GroupedLaunch:
+    """``lutgemv_grouped`` split in two: the checks and the marshalling happen here, once; the returned
+    object is called every time the launch is wanted (a few microseconds of host time per call)."""
+    return GroupedLaunch(problems, **kwargs)
+
+
 def lutgemv_grouped(problems, *, pdl=False, accumulate=False, atomic_f32=False, swiglu_f32=False):
     """Several independent mode-A products in one launch.  ``problems`` is a list
     of dicts with keys output, bWeight, alpha, bias (or None), d_input,
@@ -141,41 +206,7 @@ def lutgemv_grouped(problems, *, pdl=False, accumulate=False, atomic_f32=False, 
     ``atomic_f32=True``: every ``output`` is a float32 accumulator the product is ADDED to with fp32
     atomics (no split-K reduction tail; summation order not fixed).  ``swiglu_f32=True``: d_input and
     d_input_mul are such float32 accumulators."""
-    lib = _lib.load()
-    if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
-        raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
-    arr = (_lib.SalProblem * len(problems))()
-    dev = problems[0]["output"].device
-    n_total = 0
-    m_max = 1
-    out_dtype = torch.float32 if atomic_f32 else torch.float16
-    in_dtype = torch.float32 if swiglu_f32 else torch.float16
-    for i, p in enumerate(problems):
-        _req(p["output"], out_dtype, "output")
-        _req(p["bWeight"], torch.int32, "bWeight")
-        _req(p["alpha"], torch.float16, "alpha")
-        _req(p["d_input"], in_dtype, "d_input")
-        n, k = int(p["mSize"]), int(p["kSize"])
-        m = _rows(p["output"], p["d_input"], n, k)
-        m_max = max(m_max, m)
-        bias = p.get("bias")
-        mul = p.get("d_input_mul")      # optional: the activation is silu(d_input) * d_input_mul
-        if mul is not None:
-            _req(mul, in_dtype, "d_input_mul")
-            if mul.numel() != p["d_input"].numel():
-                raise RuntimeError("d_input_mul must have the shape of d_input")
-        arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
-                                 bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
-                                 p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]),
-                                 mul.data_ptr() if mul is not None else None)
-        n_total += n
-    flags = ((_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
-             | (_lib.SAL_OUT_F32_ATOMIC if atomic_f32 else 0) | (_lib.SAL_SWIGLU_F32 if swiglu_f32 else 0))
-    with torch.cuda.device(dev):
-        ws = workspace_for(dev, m_max, n_total)
-        stream = torch.cuda.current_stream(dev).cuda_stream
-        _lib.check(lib.sal_lutgemv_grouped(arr, len(problems), flags, ws.data_ptr(), ws.numel(), stream),
-                   "sal_lutgemv_grouped")
+    GroupedLaunch(problems, pdl=pdl, accumulate=accumulate, atomic_f32=atomic_f32, swiglu_f32=swiglu_f32)()
 
 
 def install(name: str = "lutgemm") -> None:

@@ -108,6 +108,45 @@ def test_fused_helpers_match_torch():
     assert float((out.float() - ref).abs().max()) < 4e-3
 
 
+def test_accumulator_consuming_helpers():
+    """The fp32-accumulator variants give what the fp16 helpers give on the rounded accumulator, and
+    leave every accumulator they were handed at zero."""
+    from shiftaddllm_b200 import decode_ops
+
+    g = torch.Generator(device="cuda").manual_seed(3)
+    n = 4096
+    x = torch.randn(1, n, device="cuda", generator=g).half()
+    d32 = torch.randn(1, n, device="cuda", generator=g)
+    w = (1 + 0.1 * torch.randn(n, device="cuda", generator=g)).half()
+    za, zb = torch.ones(11008, device="cuda"), torch.ones(300, device="cuda")
+    out, xo = torch.empty_like(x), torch.empty_like(x)
+    out_ref, xo_ref = torch.empty_like(x), torch.empty_like(x)
+    decode_ops.residual_rmsnorm(x, d32.half(), w, out_ref, xo_ref, 1e-5)
+    decode_ops.residual_rmsnorm_f32acc(x, d32, w, out, xo, 1e-5, za, zb)
+    assert torch.equal(xo, xo_ref) and float((out.float() - out_ref.float()).abs().max()) < 2e-3
+    assert not d32.any() and not za.any() and not zb.any()
+    decode_ops.residual_rmsnorm_f32acc(x, None, w, out, None, 1e-5)
+    decode_ops.residual_rmsnorm(x, None, w, out_ref, None, 1e-5)
+    assert float((out.float() - out_ref.float()).abs().max()) < 2e-3
+
+    heads, kvh, hd, max_len, pos_v = 8, 2, 64, 40, 9
+    q32 = torch.randn(heads * hd, device="cuda", generator=g)
+    k32 = torch.randn(kvh * hd, device="cuda", generator=g)
+    v32 = torch.randn(kvh * hd, device="cuda", generator=g)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+    ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([pos_v], device="cuda")
+    kc, vc = torch.zeros(max_len, kvh, hd, device="cuda").half(), torch.zeros(max_len, kvh, hd, device="cuda").half()
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    q_ref, k_ref, v_ref = q32.half(), k32.half(), v32.half()
+    decode_ops.rope_kv_write(q_ref, k_ref, v_ref, cos, sin, pos, kc_ref, vc_ref, heads, kvh, hd)
+    q_out = torch.empty(heads * hd, dtype=torch.float16, device="cuda")
+    decode_ops.rope_kv_write_f32acc(q32, k32, v32, q_out, cos, sin, pos, kc, vc, heads, kvh, hd)
+    assert torch.equal(q_out, q_ref) and torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+    assert not q32.any() and not k32.any() and not v32.any()
+
+
 @pytest.mark.parametrize("mode", ["torch", "fused", "atomic"])
 def test_tiny_decoder_matches_fp32_reference(mode):
     model = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, group_size=128, max_len=32, seed=1, fused=(mode != "torch"),

@@ -197,6 +197,48 @@ def test_fused_swiglu_input():
         assert o.max_rel_err(y_fused.float().cpu().numpy(), ref) <= TOL
 
 
+@pytest.mark.parametrize("k,n", [(768, 768), (4096, 4096), (11008, 4096)])
+def test_fp32_atomic_output(k, n):
+    """Opt-in fp32 output accumulated with atomics (every split adds its partial; bias added once):
+    tighter than the fp16 output because nothing is rounded to fp16, and it accumulates onto what
+    the buffer held."""
+    layer = synth.make_layer(k, n, 3, 128, packed_draw=True, bias=True, layer_index=5)
+    ref = ref_mode_a(layer)
+    base = torch.randn(1, n, generator=torch.Generator().manual_seed(2)).cuda()
+    y = base.clone()
+    prob = dict(output=y, bWeight=dev(layer.bWeight), alpha=dev(layer.alpha), bias=dev(layer.bias),
+                d_input=dev(layer.x), mSize=n, kSize=k, nb=3, num_groups=k // 128)
+    lutgemm.lutgemv_grouped([prob], atomic_f32=True)
+    torch.cuda.synchronize()
+    assert o.max_rel_err((y - base).cpu().numpy(), ref) <= 1e-4
+    assert_status_clean()
+    # refused where the fixed-order reduction is the only implementation: M > 1
+    lib = _lib.load()
+    x2 = torch.zeros(2, k, dtype=torch.float16, device="cuda")
+    y2 = torch.zeros(2, n, device="cuda")
+    rc = lib.sal_lutgemv_shift_scale(prob["bWeight"].data_ptr(), prob["alpha"].data_ptr(), None, x2.data_ptr(),
+                                     y2.data_ptr(), 2, k, n, 3, k // 128, _lib.SAL_OUT_F32_ATOMIC, None, 0,
+                                     torch.cuda.current_stream().cuda_stream)
+    assert rc == _lib.SAL_E_UNSUPPORTED
+
+
+def test_fp32_atomic_swiglu_input():
+    """down projection reading fp32 gate/up accumulators and adding into an fp32 output."""
+    import torch.nn.functional as F
+
+    layer = synth.make_layer(2048, 512, 3, 128, packed_draw=True)
+    g = torch.Generator().manual_seed(11)
+    gate, up = torch.randn(1, 2048, generator=g).cuda(), torch.randn(1, 2048, generator=g).cuda()
+    y = torch.zeros(1, 512, device="cuda")
+    lutgemm.lutgemv_grouped([dict(output=y, bWeight=dev(layer.bWeight), alpha=dev(layer.alpha), bias=None, d_input=gate,
+                                  d_input_mul=up, mSize=512, kSize=2048, nb=3, num_groups=16)],
+                            atomic_f32=True, swiglu_f32=True)
+    torch.cuda.synchronize()
+    w = o.dequant_mode_a(layer.bWeight.numpy(), layer.alpha.numpy())
+    act = (F.silu(gate) * up).half().float()          # the table build rounds the activation to fp16
+    assert o.max_rel_err(y.cpu().numpy(), o.linear_fp32(act.cpu().numpy(), w)) <= 2e-3
+
+
 def test_hand_checkable():
     k, n, q = 512, 256, 2
     bw = torch.full((k // 32, q, n), -1, dtype=torch.int32, device="cuda")          # every bit set: all +1
@@ -252,6 +294,52 @@ def test_other_entry_points():
     torch.cuda.synchronize()
     ref = o.lutgemm_compute_block_shift_int8(np.zeros((m, n)), bw_np, ai_np, x_np)
     assert o.max_rel_err(out.float().cpu().numpy(), ref) <= TOL
+
+
+@pytest.mark.parametrize("k,n,gs,q,m", [(1024, 512, 16, 3, 1), (2048, 1024, 32, 2, 1), (512, 768, 128, 4, 3),
+                                         (1024, 1024, 256, 3, 1), (1024, 1024, 512, 3, 2), (768, 1376, 16, 3, 1),
+                                         (4096, 4096, 16, 3, 1), (1024, 512, 64, 1, 5)])
+def test_block_modes_on_the_tiled_kernel(k, n, gs, q, m):
+    """Shapes the TMA-ring kernel takes in block mode (K % 256 == 0, gs a power of two >= 16 or a
+    multiple of 256): all three multiplier encodings against the dequantise oracle, and against the
+    generic kernel (same fp32 arithmetic, different summation order)."""
+    rng = np.random.default_rng(k + n + gs)
+    ng = n // gs
+    bw_np = rng.integers(-2 ** 31, 2 ** 31, (k // 32, q, n), dtype=np.int64).astype(np.int32)
+    x_np = rng.standard_normal((m, k)).astype(np.float16)
+    bias_np = (0.02 * rng.standard_normal(n)).astype(np.float16)
+    bw, x = torch.from_numpy(bw_np).cuda(), torch.from_numpy(x_np).cuda()
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def both(entry, alpha, *extra, x=x):
+        outs = []
+        for flags in (0, _lib.SAL_FORCE_GENERIC):
+            y = torch.from_numpy(np.tile(bias_np, (m, 1))).cuda()      # the reference contract: output pre-loaded, kernel adds
+            ws = lutgemm.workspace_for(y.device, m, n)
+            rc = getattr(lib, entry)(bw.data_ptr(), alpha.data_ptr(), None, x.data_ptr(), y.data_ptr(), m, k, n, q, ng, *extra,
+                                     flags | _lib.SAL_ACCUMULATE, ws.data_ptr(), ws.numel() * ws.element_size(), stream)
+            assert rc == 0
+            torch.cuda.synchronize()
+            outs.append(y.float().cpu().numpy())
+        assert o.max_rel_err(outs[0], outs[1]) <= 2e-3
+        return outs[0]
+
+    def ref(mult, xr=x_np):   # mult: fp32 [K/8, q, ng]
+        return o.linear_fp32(xr, o.dequant_mode_b(bw_np, mult), bias_np)
+
+    a16 = np.exp2(-rng.integers(2, 9, (k // 8, q, ng))).astype(np.float16) * rng.choice([1.0, 1.5, -1.25], (k // 8, q, ng)).astype(np.float16)
+    assert o.max_rel_err(both("sal_lutgemm_block", torch.from_numpy(a16).cuda()), ref(a16.astype(np.float32))) <= TOL
+    au = rng.integers(0, 512, (k // 8, q, ng)).astype(np.int16)
+    mult_u = (np.exp2(au & 7) + np.exp2((au >> 3) & 7) + np.exp2((au >> 6) & 7)).astype(np.float32)
+    xs_np = (x_np.astype(np.float32) * 0.01).astype(np.float16)     # multipliers reach 384: keep y inside fp16
+    assert o.max_rel_err(both("sal_lutgemm_block_shift", torch.from_numpy(au).cuda(), x=torch.from_numpy(xs_np).cuda()),
+                         ref(mult_u, xs_np)) <= TOL
+    ai = rng.integers(-9, -1, (k // 8, q, ng, 3)).astype(np.int8)
+    ai[::3, :, :, 2] = o.APOT_NONE
+    mult_i = np.where(ai == o.APOT_NONE, 0.0, np.exp2(ai.astype(np.float32))).sum(-1).astype(np.float32)
+    assert o.max_rel_err(both("sal_lutgemm_block_shift_int8", torch.from_numpy(ai).cuda(), 3), ref(mult_i)) <= TOL
+    assert_status_clean()
 
 
 def test_bad_calls_raise():
