@@ -329,7 +329,32 @@ def run_ours(args, rank, world, device):
     }
     if world == 1 and not args.no_cpu_baseline:
         out["cpu_baseline"] = cpu_reference(sample_layers=1, reps=5)
+    if world == 1 and not args.no_decode:
+        del launches, dep_launches, blocks
+        torch.cuda.empty_cache()
+        out["decode"] = decode_tokens_per_s(args.workload, device)
     return out
+
+
+def decode_tokens_per_s(workload, device):
+    """The other half of the metric: greedy batch-1 decode of a whole decoder of the workload's
+    architecture (random init, every linear a synthetic BCQ layer): 128 new tokens after a
+    512-token prompt (1024 for the 70B shape), the step replayed as one CUDA graph.  Reported for
+    fixed-order fp16 GEMV outputs and for the opt-in fp32 atomic accumulation."""
+    from shiftaddllm_b200 import decoder
+
+    prompt = 512 if workload == "llama2-7b" else 1024
+    with torch.cuda.device(device):
+        model = decoder.BcqLlamaDecoder(decoder.SHAPES[workload], Q, G, max_len=prompt + 2 * 128 + 16, device=device)
+        res = {}
+        for name, atomic in (("fp16_outputs", False), ("f32_atomic_outputs", True)):
+            model.set_atomic(atomic)
+            r = decoder.benchmark(model, prompt, 128)
+            res[name] = {"tokens_per_s": round(r["tokens_per_s"], 1), "ms_per_token": round(r["ms_per_token"], 4),
+                         "median_ms_per_token_synced": round(r["median_ms_per_token_synced"], 4)}
+    res["workload"] = (f"{workload}-shaped decoder, BCQ {Q}-bit g128 linears, fp16 lm_head, batch 1, {prompt}-token prompt of "
+                       "uniform random ids, 128 greedy tokens, one CUDA graph per token")
+    return res
 
 
 def read_traffic():
@@ -425,6 +450,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-decode", action="store_true", help="skip the whole-decoder tokens/s leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="fused", choices=["fused", "nccl"],
                     help="N > 1: all-gather of the output slices fused into the kernel (peer stores) or a separate NCCL call")

@@ -102,7 +102,8 @@ struct TileParams {
     int count;
     int stages;
     int accumulate;
-    int ablate;  // measurement only: bit0 skip alpha loads, bit1 skip table builds, bit2 skip lookups
+    int ablate;  // measurement only: bit0 skip alpha loads, bit1 skip table builds, bit2 skip lookups;
+                 // block mode: bit3 skip the multiplier decode + stores, bit4 skip the per-tile barrier
     int *status;
     ExchangeParams ex;
 };

@@ -119,11 +119,11 @@ class BcqLlamaDecoder:
         self._down = torch.empty(1, h, **f16)
         self._x, self._hn = torch.empty(1, h, **f16), torch.empty(1, h, **f16)
         self._attn, self._act = torch.empty(1, h, **f16), torch.empty(1, shape.ffn, **f16)
-        if atomic:
-            f32 = dict(dtype=torch.float32, device=self.device)
-            self._q32, self._k32, self._v32 = torch.zeros(1, h, **f32), torch.zeros(1, kvh * hd, **f32), torch.zeros(1, kvh * hd, **f32)
-            self._o32, self._down32 = torch.zeros(1, h, **f32), torch.zeros(1, h, **f32)
-            self._gate32, self._up32 = torch.zeros(1, shape.ffn, **f32), torch.zeros(1, shape.ffn, **f32)
+        # fp32 accumulators of the atomic mode (small; always present so that the mode can be switched later)
+        f32 = dict(dtype=torch.float32, device=self.device)
+        self._q32, self._k32, self._v32 = torch.zeros(1, h, **f32), torch.zeros(1, kvh * hd, **f32), torch.zeros(1, kvh * hd, **f32)
+        self._o32, self._down32 = torch.zeros(1, h, **f32), torch.zeros(1, h, **f32)
+        self._gate32, self._up32 = torch.zeros(1, shape.ffn, **f32), torch.zeros(1, shape.ffn, **f32)
         self.graph = None
 
     # ---- one token ------------------------------------------------------------------------
@@ -195,6 +195,13 @@ class BcqLlamaDecoder:
         self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
         self.token.copy_(self.logits.argmax().view(1))
         self.pos.add_(1)
+
+    def set_atomic(self, atomic: bool):
+        """Switches between fixed-order fp16 outputs and fp32 atomic accumulation (drops a captured graph)."""
+        self.atomic = bool(atomic)
+        self.graph = None
+        for buf in (self._q32, self._k32, self._v32, self._o32, self._down32, self._gate32, self._up32):
+            buf.zero_()
 
     def _step_atomic(self):
         """The fused step with fp32 atomic accumulation: every GEMV adds into an fp32 buffer that starts at

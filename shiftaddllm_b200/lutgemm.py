@@ -132,6 +132,27 @@ def lutgemv_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb, num_g
             flags=flags, bias=bias, alpha_numel=int(num_groups) * int(nb) * int(mSize))
 
 
+def lutgemm_block_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb, num_groups, *, pdl=False):
+    """Extension over the reference API, block (mode B) layouts: ``output = bias + product`` in one
+    kernel.  The multiplier encoding follows alpha's dtype: float16 ``[kSize/8, nb, num_groups]``,
+    int16 (three 3-bit exponents) of the same shape, or int8 ``[kSize/8, nb, num_groups, num_apot]``."""
+    flags = _lib.SAL_PDL if pdl else 0
+    numel = (int(kSize) // 8) * int(nb) * int(num_groups)
+    if alpha.dtype == torch.float16:
+        _launch("sal_lutgemm_block", output, bWeight, alpha, torch.float16, d_input, mSize, kSize, nb, num_groups,
+                flags=flags, bias=bias, alpha_numel=numel)
+    elif alpha.dtype == torch.int16:
+        _launch("sal_lutgemm_block_shift", output, bWeight, alpha, torch.int16, d_input, mSize, kSize, nb, num_groups,
+                flags=flags, bias=bias, alpha_numel=numel)
+    elif alpha.dtype == torch.int8:
+        if alpha.dim() != 4:
+            raise RuntimeError("int8 alpha must be [kSize/8, nb, num_groups, num_apot]")
+        _launch("sal_lutgemm_block_shift_int8", output, bWeight, alpha, torch.int8, d_input, mSize, kSize, nb, num_groups,
+                num_apot=alpha.shape[3], flags=flags, bias=bias, alpha_numel=numel * alpha.shape[3])
+    else:
+        raise RuntimeError(f"unsupported alpha dtype {alpha.dtype}")
+
+
 class GroupedLaunch:
     """A grouped launch whose argument block was validated and marshalled once
     (``prepare_grouped``); calling it enqueues the launch on the current stream

@@ -103,20 +103,11 @@ class LutLinear(nn.Module):
         if a.dtype == torch.float16 and self.alpha_layout == "row":
             lutgemm.lutgemv_fused(ys, self.binaryWeight, a, bias, xs, self.N, self.K, self.wbit, a.shape[0])
             return
-        # block kernels keep the reference's contract: they add into a pre-loaded output
-        if bias is not None:
-            ys.copy_(bias.unsqueeze(0).expand_as(ys))
-        else:
-            ys.zero_()
-        if a.dtype == torch.float16:
-            lutgemm.lutgemm_compute_block(ys, self.binaryWeight, a, xs, self.N, self.K, self.wbit, a.shape[2])
-        elif a.dtype == torch.int16:
-            lutgemm.lutgemm_compute_block_shift(ys, self.binaryWeight, a, xs, self.N, self.K, self.wbit, a.shape[2], 3)
-        elif a.dtype == torch.int8:
-            lutgemm.lutgemm_compute_block_shiftInt8(ys, self.binaryWeight, a, xs, self.N, self.K, self.wbit,
-                                                    a.shape[2], a.shape[3])
-        else:
+        if a.dtype not in (torch.float16, torch.int16, torch.int8):
             raise RuntimeError(f"unsupported alpha dtype {a.dtype}")
+        # block layouts: same kernels as the reference's add-into-output entry points, with the bias
+        # added by the kernel instead of a separate pre-load of the output
+        lutgemm.lutgemm_block_fused(ys, self.binaryWeight, a, bias, xs, self.N, self.K, self.wbit, a.shape[2])
 
     def extra_repr(self):
         return "in_features={}, out_features={}, bias={}, wbit={}, group_size={}".format(
