@@ -144,6 +144,9 @@ int sal_lutgemv_compute(const void *bw, const void *alpha, const void *q_bias, c
  *       (lutgemm_cuda.cpp:76-85 -> lutgemm_cuda_kernel.cu:380-408 -> mv_fp16_bias.hpp:342-495);
  *       this is the call LutLinear.forward makes (lut_gemm/quant.py:50-51).
  * x fp16 [M][K], y fp16 [M][N], 1 <= M <= SAL_MAX_M.
+ * Shapes with K % 256 == 0, N % 8 == 0, q <= 4 and N/num_groups = 16, 32, 64 (then num_groups % 4 == 0),
+ * 128 or a multiple of 256 (int8: num_apot == 3) run on the TMA-ring kernel with a per-lookup multiplier
+ * table in shared memory; all other shapes on the generic kernel (also selected by SAL_FORCE_GENERIC).
  */
 int sal_lutgemm_block(const void *bw, const void *alpha, const void *bias, const void *x, void *y,
                       int M, int K, int N, int q, int num_groups, unsigned flags,
@@ -225,7 +228,9 @@ int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_in
  * (100 = one CTA per SM, 200 = two, 0 = automatic); "full_sm" lets a CTA use a
  * whole SM's shared memory (one CTA per SM, deeper ring); "abs" 0/1 forces the table
  * addressing variant; "ablate" bit0/1/2 skips alpha loads / table builds /
- * lookups (results are then meaningless; used to time the parts). */
+ * lookups, bit3/4 the multiplier stores / per-tile barrier of the block mode
+ * (results are then meaningless; used to time the parts); "force_per" and
+ * "force_splits" override the planner's column tiles per CTA and K splits. */
 int sal_debug_set(const char *key, int value);
 
 #ifdef __cplusplus
