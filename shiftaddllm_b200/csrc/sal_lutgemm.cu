@@ -33,6 +33,7 @@
 
 #include <cuda.h>
 #include <cuda_fp16.h>
+#include <mutex>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -72,8 +73,10 @@ struct TileProblem {
     int g;               // group size along K, multiple of 128
     int kblocks;         // K / 256
     int nsub_total;      // ceil(N / CW)
-    int nsub_per_range;
-    int ranges, splits;
+    int nsub_per_range;  // column tiles per range (the last range may be narrower)
+    int ranges;
+    int splits;          // CTAs per full-width range
+    int splits_last;     // CTAs of the last range
     int cta_begin;
     // block mode (one multiplier per 8 input features x `blk_gs` output columns, alpha [K/8][q][N/blk_gs]):
     int blk_kind;     // 0 = off (alpha per K group and column), else the AlphaKind of the multipliers
@@ -372,16 +375,25 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     for (int i = 1; i < P.count; ++i)
         if ((int)blockIdx.x >= P.p[i].cta_begin) pi = i;
     const TileProblem &pr = P.p[pi];
+    // Work of a column range = its (K block, column tile) units in K-block-major order; the range's CTAs
+    // take equal contiguous runs of that sequence, so a CTA may start and end in the middle of a K block.
     const int local = blockIdx.x - pr.cta_begin;
-    const int range = local % pr.ranges;
-    const int split = local / pr.ranges;
+    const int full_ctas = (pr.ranges - 1) * pr.splits;
+    const bool in_last = local >= full_ctas;
+    const int range = in_last ? pr.ranges - 1 : local / pr.splits;
+    const int split = in_last ? local - full_ctas : local % pr.splits;
+    const int S = in_last ? pr.splits_last : pr.splits;  // CTAs sharing this range
     const int N = pr.N;
     const int row0 = (int)blockIdx.y * ROWS;
     const int rows_here = min(ROWS, pr.M - row0);
     const int sub_begin = range * pr.nsub_per_range;
     const int nsub = min(pr.nsub_per_range, pr.nsub_total - sub_begin);
-    const int kb_begin = (int)(((long long)split * pr.kblocks) / pr.splits);
-    const int kb_end = (int)(((long long)(split + 1) * pr.kblocks) / pr.splits);
+    const int units = nsub * pr.kblocks;
+    const int u_begin = (int)(((long long)split * units) / S);
+    const int u_end = (int)(((long long)(split + 1) * units) / S);   // > u_begin: the planner keeps S <= units
+    const int kb_begin = u_begin / nsub, t_first = u_begin % nsub;   // first K block and its first tile
+    const int kb_last = (u_end - 1) / nsub, t_last = (u_end - 1) % nsub;
+    const int kb_end = kb_last + 1;
 
     if (tid == 0) {
         for (int s = 0; s < stages; ++s) {
@@ -399,7 +411,8 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         uint32_t phase = 0;  // parity of the consumers' release being waited for (previous use of the stage)
         bool first_round = true;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-            for (int sub = 0; sub < nsub; ++sub) {
+            const int s_lo = kb == kb_begin ? t_first : 0, s_hi = kb == kb_last ? t_last + 1 : nsub;
+            for (int sub = s_lo; sub < s_hi; ++sub) {
                 if (!first_round) mbar_wait(empty0 + 8 * st, phase, P.status);
                 const int n0 = (sub_begin + sub) * CW;
                 const uint32_t full = full0 + 8 * st;
@@ -490,7 +503,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         }
     };
     __half a_next[2][Q];
-    if (!BLK && kb_begin < kb_end && !(P.ablate & 1)) load_alpha(kb_begin, 0, a_next);  // constants: legal before the dependency wait
+    if (!BLK && kb_begin < kb_end && !(P.ablate & 1)) load_alpha(kb_begin, t_first, a_next);  // constants: legal before the dependency wait
     else {
 #pragma unroll
         for (int b = 0; b < Q; ++b) a_next[0][b] = a_next[1][b] = __float2half(0.f);
@@ -588,7 +601,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         }
     };
     if constexpr (BLK) {
-        if (kb_begin < kb_end) load_block_alpha(kb_begin, 0, raw_next);
+        if (kb_begin < kb_end) load_block_alpha(kb_begin, t_first, raw_next);
     }
     uint32_t mbuf = 0;  // byte offset of the multiplier buffer the current tile uses (two buffers, alternating)
 
@@ -620,15 +633,16 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
         // unrolling it over the column tiles overflows the instruction cache.  acc[] is then
         // indexed dynamically and lives in (L1-resident) local memory: two accesses per tile.
+        const int s_lo = kb == kb_begin ? t_first : 0, s_hi = kb == kb_last ? t_last + 1 : nsub;
 #pragma unroll 1
-        for (int sub = 0; sub < nsub; ++sub) {
+        for (int sub = s_lo; sub < s_hi; ++sub) {
             __half a_cur[2][Q];
 #pragma unroll
             for (int hp = 0; hp < 2; ++hp)
 #pragma unroll
                 for (int b = 0; b < Q; ++b) a_cur[hp][b] = a_next[hp][b];
             {
-                const bool more_sub = (sub + 1 < nsub);
+                const bool more_sub = (sub + 1 < s_hi);
                 const int kb_n = more_sub ? kb : kb + 1;
                 if constexpr (BLK) {
                     uint32_t raw_cur[NVI][NVW];
@@ -769,15 +783,16 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
 #pragma unroll
         for (int sub = 0; sub < MAX_SUB; ++sub) {
             const int n = (sub_begin + sub) * CW + col;
-            if (sub < nsub && n < N) {
+            const bool touched = kb_begin != kb_last ? true : (sub >= t_first && sub <= t_last);
+            if (sub < nsub && n < N && touched) {
                 float v = acc[0][sub];
-                if (split == 0 && pr.bias) v += __half2float(pr.bias[n]);
+                if (pr.bias && u_begin <= sub && sub < u_end) v += __half2float(pr.bias[n]);  // the CTA holding unit (K block 0, sub)
                 atomicAdd(yacc + n, v);
             }
         }
         return;
     }
-    if (pr.splits == 1) {
+    if (S == 1) {
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             if (r < rows_here) {
@@ -807,12 +822,12 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         return;
     }
     // partial sums: [activation row][K split][N]; arrival counters: [row pair][column range]
-    const int S = pr.splits;
+    const int SP = max(pr.splits, pr.splits_last);  // stride of the partial sums: [row][SP][N]
     unsigned *counter = pr.counters + (size_t)blockIdx.y * pr.ranges + range;
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
         if (r < rows_here) {
-            float *prow = pr.partials + ((size_t)(row0 + r) * S + split) * N;
+            float *prow = pr.partials + ((size_t)(row0 + r) * SP + split) * N;
 #pragma unroll
             for (int sub = 0; sub < MAX_SUB; ++sub) {
                 const int n = (sub_begin + sub) * CW + col;
@@ -834,7 +849,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         // = 64 independent L2 loads are in flight per thread, so the whole reduction costs one
         // or two round trips instead of one per column tile.
         for (int r = 0; r < rows_here; ++r) {
-            const float *pbase = pr.partials + (size_t)(row0 + r) * S * N;
+            const float *pbase = pr.partials + (size_t)(row0 + r) * SP * N;
             __half *yrow = pr.y + (size_t)(row0 + r) * N;
             for (int sub0 = 0; sub0 < nsub; sub0 += 4) {
                 float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -1094,37 +1109,123 @@ inline bool aligned(const void *p, size_t a) { return (reinterpret_cast<uintptr_
 int g_force_per = 0, g_force_splits = 0;  // measurement hooks: override the planner's choice
 
 struct Plan {
-    int ranges, splits, nsub_per_range, nsub_total, kblocks;
+    int ranges, splits, splits_last, nsub_per_range, nsub_total, kblocks;
+    int ctas;
+    double cost;
 };
 
-// Chooses column ranges x K splits for one problem.  `slots` is the number of CTAs of this
-// problem that can be resident at once (its share of SMs x CTAs per SM).  Work unit = one
-// 256-feature K block x one column tile; building the tables of a K block costs about 0.25
-// units; CTAs beyond `slots` run as later waves and restart the pipeline.
-Plan plan_problem(int K, int N, int slots, bool allow_split, int cw) {
-    Plan best{};
+// Estimated time of one CTA, in units of (one 256-feature K block x one 256-column tile): `n` units of a
+// range `w` tiles wide that `c` CTAs share.  Building the tables of a K block costs about 0.25 units (a run
+// of n units touches about n / w + 1 blocks once it no longer starts on a block boundary); the split-K tail
+// grows with the number of partial sums.  Calibrated on sweeps over the launch shapes of a LLaMA-2-7B block.
+double g_cost_tb = 0.25, g_cost_r0 = 0.5, g_cost_r1 = 0.05, g_cost_rw = 0.025;  // model constants (sal_debug_set can override)
+double cta_cost(double n, int w, int c) {
+    double cost = n + g_cost_tb * (n / w + (c > 1 ? 1.0 : 0.0));
+    if (c > 1) cost += g_cost_r0 + g_cost_r1 * c + g_cost_rw * c * w;
+    return cost;
+}
+
+// Fewest CTAs with which one problem stays within `bound` (estimated time per CTA), over all range widths.
+// Returns false if no width does.
+bool plan_problem(int K, int N, double bound, bool allow_split, int cw, Plan *out) {
     const int nsub_total = (N + cw - 1) / cw;
     const int kblocks = K / KB_FEATS;
-    double best_cost = 1e30;
+    // smallest number of CTAs for a range of `units` units, `w` tiles wide; 0 = impossible
+    const auto ctas_for = [&](int units, int w, double *cost) {
+        const int cmax = allow_split ? (units < MAX_SPLIT ? units : MAX_SPLIT) : 1;
+        for (int c = 1; c <= cmax; ++c) {
+            if (g_force_splits > 0 && allow_split && c != (g_force_splits < cmax ? g_force_splits : cmax)) continue;
+            const double t = cta_cost((double)((units + c - 1) / c), w, c);
+            if (t <= bound) {
+                *cost = t;
+                return c;
+            }
+        }
+        return 0;
+    };
+    bool found = false;
+    Plan best{};
     for (int per = 1; per <= MAX_SUB && per <= nsub_total; ++per) {
         if (g_force_per > 0 && per != (g_force_per < nsub_total ? g_force_per : nsub_total)) continue;
         const int ranges = (nsub_total + per - 1) / per;
-        const int smax = allow_split ? (kblocks < MAX_SPLIT ? kblocks : MAX_SPLIT) : 1;
-        for (int splits = 1; splits <= smax; ++splits) {
-            if (g_force_splits > 0 && allow_split && splits != (g_force_splits < smax ? g_force_splits : smax)) continue;
-            const int ctas = ranges * splits;
-            const int kb_per = (kblocks + splits - 1) / splits;
-            const int waves = (ctas + slots - 1) / slots;
-            // calibrated on a sweep of (per, splits) over the four launch shapes of a LLaMA-2-7B block
-            double cost = waves * (kb_per * (per + 0.25)) + 2.0 * (waves - 1);
-            cost += splits > 1 ? 0.5 + 0.05 * splits : 0.0;  // reduction tail grows with the number of partial sums
-            if (cost < best_cost) {
-                best_cost = cost;
-                best = Plan{ranges, splits, per, nsub_total, kblocks};
-            }
+        const int w_last = nsub_total - (ranges - 1) * per;
+        double cost_full = 0.0, cost_last = 0.0;
+        const int c_last = ctas_for(w_last * kblocks, w_last, &cost_last);
+        const int c_full = ranges > 1 ? ctas_for(per * kblocks, per, &cost_full) : 1;
+        if (c_last == 0 || c_full == 0) continue;
+        const int ctas = (ranges - 1) * c_full + c_last;
+        const double cost = cost_full > cost_last ? cost_full : cost_last;
+        if (!found || ctas < best.ctas || (ctas == best.ctas && cost < best.cost)) {
+            best = Plan{ranges, ranges > 1 ? c_full : c_last, c_last, per, nsub_total, kblocks, ctas, cost};
+            found = true;
         }
     }
-    return best;
+    if (found) *out = best;
+    return found;
+}
+
+// Plans all problems of a launch: the smallest bound on the per-CTA time for which the launch fits into
+// `slots` resident CTAs (bisection; every CTA of every problem then has about the same amount of work).
+// If not even single-CTA ranges fit, the launch runs in several waves.
+bool plan_group_once(const sal_problem *problems, int count, int slots, bool allow_split, int cw, double bound, Plan *plans,
+                     int *total) {
+    *total = 0;
+    for (int i = 0; i < count; ++i) {
+        if (!plan_problem(problems[i].K, problems[i].N, bound, allow_split, cw, &plans[i])) return false;
+        *total += plans[i].ctas;
+    }
+    return *total <= slots;
+}
+
+struct PlanCacheEntry {
+    unsigned long long key;
+    int count;
+    Plan plans[SAL_MAX_GROUP];
+};
+PlanCacheEntry g_plan_cache[256];
+std::mutex g_plan_mutex;
+
+void plan_group(const sal_problem *problems, int count, int slots, bool allow_split, int cw, Plan *plans) {
+    // the plan depends on the shapes only: remember it (planning costs a few hundred microseconds)
+    unsigned long long key = 1469598103934665603ull;
+    const auto mix = [&](long long v) { key = (key ^ (unsigned long long)v) * 1099511628211ull; };
+    mix(count), mix(slots), mix(allow_split), mix(cw), mix(g_force_per), mix(g_force_splits);
+    for (int i = 0; i < count; ++i) mix(problems[i].K), mix(problems[i].N);
+    PlanCacheEntry &slot = g_plan_cache[key & 255];
+    {
+        std::lock_guard<std::mutex> lock(g_plan_mutex);
+        if (slot.key == key && slot.count == count) {
+            for (int i = 0; i < count; ++i) plans[i] = slot.plans[i];
+            return;
+        }
+    }
+    double units_total = 0, hi = 0;
+    for (int i = 0; i < count; ++i) {
+        const double u = (double)((problems[i].N + cw - 1) / cw) * (problems[i].K / KB_FEATS);
+        units_total += u;
+        const double worst = cta_cost((problems[i].K / KB_FEATS) * (double)MAX_SUB, 1, 1) + 4.0;
+        if (worst > hi) hi = worst;
+    }
+    int total = 0;
+    for (int waves = 1;; ++waves) {
+        if (plan_group_once(problems, count, slots * waves, allow_split, cw, hi, plans, &total)) {
+            double lo = units_total / (slots * waves);
+            double up = hi;
+            for (int it = 0; it < 40 && up - lo > 0.01; ++it) {
+                const double mid = 0.5 * (lo + up);
+                Plan trial[SAL_MAX_GROUP];
+                if (plan_group_once(problems, count, slots * waves, allow_split, cw, mid, trial, &total)) up = mid;
+                else lo = mid;
+            }
+            plan_group_once(problems, count, slots * waves, allow_split, cw, up, plans, &total);
+            break;
+        }
+        if (waves >= 64) break;  // cannot happen for shapes that passed validation; plans hold the last attempt
+    }
+    std::lock_guard<std::mutex> lock(g_plan_mutex);
+    slot.key = key;
+    slot.count = count;
+    for (int i = 0; i < count; ++i) slot.plans[i] = plans[i];
 }
 
 int stage_bytes_for(int q, int ncw) { return KB_WORDS * q * ncw * 32 * 4; }
@@ -1353,21 +1454,19 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
     }
     int writers = 0;
 
-    // CTA budget per problem, proportional to its weight volume
-    double units_total = 0;
-    for (int i = 0; i < count; ++i)
-        units_total += (double)((problems[i].N + cw - 1) / cw) * (problems[i].K / KB_FEATS);
+    // every CTA of the launch gets about the same amount of work, whatever problem it belongs to
+    const bool have_ws = workspace != nullptr && ws_bytes >= WS_PARTIAL_OFFSET;
+    const int pct = g_budget_pct > 0 ? g_budget_pct : 100 * ctas_per_sm;
+    int slots = (int)(sms * (pct / 100.0) / row_groups);   // row groups share the SMs
+    if (slots < 4 * count) slots = 4 * count;
+    Plan plans[SAL_MAX_GROUP];
+    plan_group(problems, count, slots, have_ws || atomic_out, cw, plans);
     int cta = 0;
     int counter_off = 0;
     size_t n_off = 0;
-    const bool have_ws = workspace != nullptr && ws_bytes >= WS_PARTIAL_OFFSET;
     for (int i = 0; i < count; ++i) {
         const sal_problem &sp = problems[i];
-        const double units = (double)((sp.N + cw - 1) / cw) * (sp.K / KB_FEATS);
-        const int pct = g_budget_pct > 0 ? g_budget_pct : 100 * ctas_per_sm;
-        int budget = (int)(sms * (pct / 100.0) * units / units_total / row_groups + 0.5);  // row groups share the SMs
-        if (budget < 4) budget = 4;
-        Plan pl = plan_problem(sp.K, sp.N, budget, have_ws || atomic_out, cw);
+        const Plan &pl = plans[i];
         TileProblem &tp = P.p[i];
         tp.bw = reinterpret_cast<const uint32_t *>(sp.bw);
         tp.alpha = reinterpret_cast<const __half *>(sp.alpha);
@@ -1390,6 +1489,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         tp.nsub_per_range = pl.nsub_per_range;
         tp.ranges = pl.ranges;
         tp.splits = pl.splits;
+        tp.splits_last = pl.splits_last;
         tp.cta_begin = cta;
         tp.gather_off = ex ? (long long)ex->gather_offsets[i] : 0;
         writers += pl.ranges;  // one CTA per column range stores final outputs
@@ -1397,7 +1497,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
             const int erc = encode_weight_map(&P.tmap[i], sp.bw, sp.K, sp.N, sp.q);
             if (erc != SAL_OK) return erc;
         }
-        if (pl.splits > 1 && !atomic_out) {
+        if ((pl.splits > 1 || pl.splits_last > 1) && !atomic_out) {
             if (counter_off + pl.ranges * row_groups > WS_MAX_COUNTERS) return SAL_E_WORKSPACE;
             const size_t need = WS_PARTIAL_OFFSET + (n_off + (size_t)sp.N) * (size_t)M * MAX_SPLIT * sizeof(float);
             if (!info_only && need > ws_bytes) return SAL_E_WORKSPACE;
@@ -1406,7 +1506,7 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
             counter_off += pl.ranges * row_groups;
         }
         n_off += (size_t)sp.N;
-        cta += pl.ranges * pl.splits;
+        cta += pl.ctas;
     }
     if (writers_out) *writers_out = writers;
     if (info_only) {
@@ -1507,7 +1607,15 @@ int sal_debug_set(const char *key, int value) {
     else if (eq("force_per")) g_force_per = value;
     else if (eq("force_splits")) g_force_splits = value;
     else if (eq("budget_pct")) g_budget_pct = value > 0 ? value : 0;
+    else if (eq("cost_tb")) g_cost_tb = value / 1000.0;
+    else if (eq("cost_r0")) g_cost_r0 = value / 1000.0;
+    else if (eq("cost_r1")) g_cost_r1 = value / 1000.0;
+    else if (eq("cost_rw")) g_cost_rw = value / 1000.0;
     else return SAL_E_UNSUPPORTED;
+    {
+        std::lock_guard<std::mutex> lock(g_plan_mutex);   // remembered plans were made under the old settings
+        for (auto &e : g_plan_cache) e.key = 0, e.count = 0;
+    }
     return SAL_OK;
 }
 
