@@ -48,6 +48,17 @@ int sal_rope_kv_write_f32acc(void *q_f32, void *k_f32, void *v_f32, void *q_out,
 int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
                              int heads, int kv_heads, int hd, int max_len, float scale, void *stream);
 
+/* The same attention split over the cached positions (kv_heads x up to 32 CTAs instead of one CTA per head;
+ * a K / V row is read once for all query heads of its group) with the slices merged by the last CTA of a
+ * kv head to finish.  hd in {32, 64, 128, 256}, heads / kv_heads in {1, 2, 4, 8}, caches 16-byte aligned;
+ * other shapes return SAL_E_UNSUPPORTED (use sal_attention_decode_f16).  `workspace`: caller-owned scratch of
+ * sal_attention_workspace_bytes(heads, hd) bytes, zero-filled once (arrival counters reset themselves), not
+ * shared between streams. */
+size_t sal_attention_workspace_bytes(int heads, int hd);
+int sal_attention_decode_split_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
+                                   int heads, int kv_heads, int hd, int max_len, float scale, void *workspace,
+                                   size_t workspace_bytes, void *stream);
+
 /* out = silu(gate) * up, fp16 vectors of n elements. */
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream);
 

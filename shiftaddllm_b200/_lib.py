@@ -64,6 +64,8 @@ SIGNATURES = {
     "sal_residual_rmsnorm_f32acc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _vp, _i, _vp, _i, _vp]),
     "sal_rope_kv_write_f32acc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "sal_attention_decode_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp]),
+    "sal_attention_workspace_bytes": (ctypes.c_size_t, [_i, _i]),
+    "sal_attention_decode_split_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp, ctypes.c_size_t, _vp]),
     "sal_silu_mul_f16": (_i, [_vp, _vp, _vp, _i, _vp]),
 }
 

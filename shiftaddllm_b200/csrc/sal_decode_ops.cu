@@ -270,6 +270,270 @@ int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, voi
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...) == cudaSuccess ? SAL_OK : SAL_E_LAUNCH;
 }
 
+
+// Single-query attention split over the cached positions ("flash decoding"): CTA (kv head, slice) handles
+// the slice's positions for the G query heads that share the kv head, so a K or V row is read once per
+// group.  A row of hd halves is read by hd/8 lanes with 16-byte loads (a warp covers 32/(hd/8) positions
+// per load instruction, four instructions in flight).  Every CTA leaves (max, sum, unnormalised output)
+// per query head in the scratch buffer; the last CTA of a kv head to arrive merges the slices.
+constexpr int ATTN_MAX_SPLIT = 32;
+constexpr int ATTN_WARPS = 8;
+
+// STAGE_V: the slice's V rows are fetched together with its K rows and parked in shared memory, so the
+// second pass does not wait for memory again (used when the slice fits).
+template <int G, bool STAGE_V>
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const __half *q, const __half *k_cache,
+                                                                          const __half *v_cache, const int64_t *pos_p,
+                                                                          __half *out, float *partial, unsigned *counters,
+                                                                          int kv_heads, int hd, int max_len, float scale,
+                                                                          int nsplit, int slice_cap) {
+    extern __shared__ float smem_f[];
+    __shared__ float s_m[G], s_l[G];
+    __shared__ float s_w[ATTN_MAX_SPLIT][G];
+    __shared__ int s_is_last;
+    pdl_prologue();
+    constexpr int NW = ATTN_WARPS, U = 4;
+    float *qf = smem_f;                  // [G][hd], pre-scaled
+    float *sc = qf + G * hd;             // [G][slice_cap]
+    float *obuf = sc + G * slice_cap;    // [NW][G][hd]
+    uint4 *vs = reinterpret_cast<uint4 *>(obuf + NW * G * hd);   // STAGE_V: [slice_cap][hd / 8] 16-byte pieces of the V rows
+    const int kvh = blockIdx.x, split = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    int64_t pos = *pos_p;
+    if (pos >= max_len) pos = max_len - 1;
+    const int T = (int)pos + 1;
+    const int per = (T + nsplit - 1) / nsplit;
+    const int t_begin = split * per;
+    const int n = max(0, min(T, t_begin + per) - t_begin);   // positions of this slice (<= slice_cap)
+    const int lpr = hd >> 3;             // lanes per row (hd is a power of two: 4, 8, 16 or 32 lanes)
+    const int lpr_shift = 31 - __clz(lpr), hd_shift = lpr_shift + 3;
+    const int rows = 32 >> lpr_shift;    // positions per warp and load instruction
+    const int sub = lane >> lpr_shift, sl = lane & (lpr - 1);
+    for (int i = tid; i < G * hd; i += blockDim.x) qf[i] = __half2float(q[(size_t)kvh * G * hd + i]) * scale;
+    __syncthreads();
+    const size_t row_stride = (size_t)kv_heads * hd;
+    const __half *kbase = k_cache + ((size_t)t_begin * kv_heads + kvh) * hd + sl * 8;
+    const __half *vbase = v_cache + ((size_t)t_begin * kv_heads + kvh) * hd + sl * 8;
+    // ---- scores
+    {
+        float qr[G][8];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) qr[g][j] = qf[g * hd + sl * 8 + j];
+        for (int base = warp * rows; base < n; base += NW * rows * U) {
+            uint4 kk[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int tl = base + u * NW * rows + sub;
+                kk[u] = tl < n ? *reinterpret_cast<const uint4 *>(kbase + (size_t)tl * row_stride) : make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (STAGE_V) {
+                uint4 vv[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int tl = base + u * NW * rows + sub;
+                    vv[u] = tl < n ? *reinterpret_cast<const uint4 *>(vbase + (size_t)tl * row_stride) : make_uint4(0u, 0u, 0u, 0u);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int tl = base + u * NW * rows + sub;
+                    if (tl < n) vs[tl * lpr + sl] = vv[u];
+                }
+            }
+            // all U x G partial dot products first, then the butterfly over the row's lanes on all of them
+            // together (independent shuffles pipeline; one value at a time they would serialise on latency)
+            float d[U][G];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const __half2 *h = reinterpret_cast<const __half2 *>(&kk[u]);
+                float kf[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h[j]);
+                    kf[2 * j] = f.x;
+                    kf[2 * j + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc += qr[g][j] * kf[j];
+                    d[u][g] = acc;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                if (o < lpr) {
+#pragma unroll
+                    for (int u = 0; u < U; ++u)
+#pragma unroll
+                        for (int g = 0; g < G; ++g) d[u][g] += __shfl_xor_sync(0xffffffffu, d[u][g], o);
+                }
+            }
+            if (sl == 0) {
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int tl = base + u * NW * rows + sub;
+                    if (tl < n) {
+#pragma unroll
+                        for (int g = 0; g < G; ++g) sc[g * slice_cap + tl] = d[u][g];
+                    }
+                }
+            }
+        }
+    }
+    __syncthreads();
+    // ---- slice maximum and sum per query head (one warp per head, round robin)
+    for (int g = warp; g < G; g += NW) {
+        float m = -INFINITY;
+        for (int t = lane; t < n; t += 32) m = fmaxf(m, sc[g * slice_cap + t]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int t = lane; t < n; t += 32) {
+            const float pe = __expf(sc[g * slice_cap + t] - m);
+            sc[g * slice_cap + t] = pe;
+            l += pe;
+        }
+        l = warp_sum(l);
+        if (lane == 0) {
+            s_m[g] = m;
+            s_l[g] = l;
+        }
+    }
+    __syncthreads();
+    // ---- weighted sum of the V rows
+    {
+        float o[G][8];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[g][j] = 0.f;
+        for (int base = warp * rows; base < n; base += NW * rows * U) {
+            uint4 vv[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int tl = base + u * NW * rows + sub;
+                if (STAGE_V) vv[u] = tl < n ? vs[tl * lpr + sl] : make_uint4(0u, 0u, 0u, 0u);
+                else vv[u] = tl < n ? *reinterpret_cast<const uint4 *>(vbase + (size_t)tl * row_stride) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int tl = base + u * NW * rows + sub;
+                const __half2 *h = reinterpret_cast<const __half2 *>(&vv[u]);
+                float vf[8];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h[j]);
+                    vf[2 * j] = f.x;
+                    vf[2 * j + 1] = f.y;
+                }
+#pragma unroll
+                for (int g = 0; g < G; ++g) {
+                    const float pe = tl < n ? sc[g * slice_cap + tl] : 0.f;
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o[g][j] += pe * vf[j];
+                }
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float v = o[g][j];
+#pragma unroll
+                for (int off = 16; off >= 4; off >>= 1)
+                    if (off >= lpr) v += __shfl_xor_sync(0xffffffffu, v, off);
+                if (sub == 0) obuf[(warp * G + g) * hd + sl * 8 + j] = v;
+            }
+    }
+    __syncthreads();
+    // ---- this slice's result: per query head hd unnormalised outputs, then max and sum
+    const int stride = hd + 2;
+    float *mine = partial + ((size_t)(kvh * nsplit + split) * G) * stride;
+    for (int i = tid; i < G * hd; i += blockDim.x) {
+        const int g = i >> hd_shift, d = i & (hd - 1);
+        float r = 0.f;
+#pragma unroll
+        for (int w = 0; w < NW; ++w) r += obuf[(w * G + g) * hd + d];
+        __stcg(mine + g * stride + d, r);
+    }
+    if (tid < G) {
+        __stcg(mine + tid * stride + hd, s_m[tid]);
+        __stcg(mine + tid * stride + hd + 1, s_l[tid]);
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_is_last = (atomicAdd(counters + kvh, 1u) == (unsigned)(nsplit - 1));
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence();
+    const float *all = partial + ((size_t)kvh * nsplit * G) * stride;
+    // weight of every slice per query head: exp(slice max - overall max) / overall sum (empty slices: 0)
+    // (one warp per query head, lane = slice: all loads of a head are in flight together)
+    for (int g = warp; g < G; g += NW) {
+        float m_sp = -INFINITY, l_sp = 0.f;
+        if (lane < nsplit) {
+            const float *ps = all + (size_t)(lane * G + g) * stride;
+            m_sp = __ldcg(ps + hd);
+            l_sp = __ldcg(ps + hd + 1);
+        }
+        const float m = warp_max(m_sp);
+        const float wgt = lane < nsplit ? __expf(m_sp - m) : 0.f;
+        const float l = warp_sum(wgt * l_sp);
+        if (lane < nsplit) s_w[lane][g] = wgt / l;
+    }
+    __syncthreads();
+    for (int i = tid; i < G * hd; i += blockDim.x) {
+        const int g = i >> hd_shift, d = i & (hd - 1);
+        float acc = 0.f;
+        for (int s0 = 0; s0 < nsplit; s0 += 8) {
+            float t[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = (s0 + k < nsplit) ? __ldcg(all + (size_t)((s0 + k) * G + g) * stride + d) : 0.f;
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc += (s0 + k < nsplit) ? s_w[s0 + k][g] * t[k] : 0.f;
+        }
+        out[((size_t)kvh * G + g) * hd + d] = __float2half_rn(acc);
+    }
+    if (tid == 0) counters[kvh] = 0u;   // ready for the next call
+}
+
+constexpr size_t ATTN_WS_HEADER = 1024;   // arrival counters, one per kv head (<= 256 heads)
+
+template <int G, bool STAGE_V>
+int launch_attention_variant(size_t smem, const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
+                             int kv_heads, int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap,
+                             cudaStream_t stream) {
+    if (smem + 2048 > 48 * 1024) {   // the kernel's static shared memory counts against the default limit too
+        static size_t configured = 0;
+        if (configured < smem) {
+            if (cudaFuncSetAttribute(attention_split_kernel<G, STAGE_V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+                cudaSuccess)
+                return SAL_E_LAUNCH;
+            configured = smem;
+        }
+    }
+    return launch_pdl(attention_split_kernel<G, STAGE_V>, dim3(kv_heads, nsplit), dim3(ATTN_WARPS * 32), smem, stream,
+                      reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k_cache),
+                      reinterpret_cast<const __half *>(v_cache), pos, reinterpret_cast<__half *>(out),
+                      reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + ATTN_WS_HEADER),
+                      reinterpret_cast<unsigned *>(workspace), kv_heads, hd, max_len, scale, nsplit, slice_cap);
+}
+
+template <int G>
+int launch_attention_split(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int kv_heads,
+                           int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap, cudaStream_t stream) {
+    const size_t base = (size_t)(G * hd + G * slice_cap + ATTN_WARPS * G * hd) * sizeof(float);
+    const size_t staged = base + (size_t)slice_cap * hd * sizeof(__half);
+    if (staged <= 96 * 1024)
+        return launch_attention_variant<G, true>(staged, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace,
+                                                 nsplit, slice_cap, stream);
+    if (base > 200 * 1024) return SAL_E_UNSUPPORTED;
+    return launch_attention_variant<G, false>(base, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit,
+                                              slice_cap, stream);
+}
+
 }  // namespace
 
 extern "C" {
@@ -336,6 +600,37 @@ int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_c
     return launch_pdl(attention_decode_kernel, dim3(heads), dim3(1024), smem, stream, reinterpret_cast<const __half *>(q),
                       reinterpret_cast<const __half *>(k_cache), reinterpret_cast<const __half *>(v_cache), pos,
                       reinterpret_cast<__half *>(out), heads, kv_heads, hd, max_len, scale);
+}
+
+size_t sal_attention_workspace_bytes(int heads, int hd) {
+    if (heads < 1 || hd < 1) return 0;
+    return ATTN_WS_HEADER + (size_t)heads * ATTN_MAX_SPLIT * (size_t)(hd + 2) * sizeof(float);
+}
+
+int sal_attention_decode_split_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
+                                   int heads, int kv_heads, int hd, int max_len, float scale, void *workspace,
+                                   size_t workspace_bytes, void *stream) {
+    if (!q || !k_cache || !v_cache || !pos || !out || !workspace) return SAL_E_NULL;
+    if (heads < 1 || kv_heads < 1 || kv_heads > 256 || heads % kv_heads || max_len < 1 || max_len > 65536) return SAL_E_SHAPE;
+    if (hd != 32 && hd != 64 && hd != 128 && hd != 256) return SAL_E_UNSUPPORTED;
+    if (workspace_bytes < sal_attention_workspace_bytes(heads, hd)) return SAL_E_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return SAL_E_ALIGN;
+    const int G = heads / kv_heads;
+    // about three CTAs per SM (they are small), at least ~16 positions per slice at the longest context
+    int nsplit = (444 + kv_heads - 1) / kv_heads;
+    if (nsplit > ATTN_MAX_SPLIT) nsplit = ATTN_MAX_SPLIT;
+    if (G >= 8 && nsplit > ATTN_MAX_SPLIT / 2) nsplit = ATTN_MAX_SPLIT / 2;   // the merge grows with G x slices (measured)
+    if (nsplit > (max_len + 15) / 16) nsplit = (max_len + 15) / 16;
+    if (nsplit < 1) nsplit = 1;
+    const int slice_cap = (max_len + nsplit - 1) / nsplit;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    switch (G) {
+        case 1: return launch_attention_split<1>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
+        case 2: return launch_attention_split<2>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
+        case 4: return launch_attention_split<4>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
+        case 8: return launch_attention_split<8>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
+        default: return SAL_E_UNSUPPORTED;
+    }
 }
 
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream) {

@@ -45,8 +45,24 @@ def rope_kv_write_f32acc(q32, k32, v32, q_out, cos, sin, pos, k_cache, v_cache, 
                                             kv_heads, hd, k_cache.shape[0], _stream(q_out)), "sal_rope_kv_write_f32acc")
 
 
-def attention_decode(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, scale: float):
+def attention_workspace(heads: int, hd: int, device) -> torch.Tensor:
+    """Zero-filled scratch for the split form of attention_decode (one per stream that uses it)."""
     lib = _lib.load()
+    return torch.zeros(lib.sal_attention_workspace_bytes(int(heads), int(hd)), dtype=torch.uint8, device=device)
+
+
+def attention_decode(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, scale: float, workspace=None):
+    """Single-query attention over cache positions 0..pos.  With a `workspace` (attention_workspace) the
+    positions are split over many CTAs and merged; shapes that form does not take fall back to one CTA
+    per head."""
+    lib = _lib.load()
+    if workspace is not None:
+        rc = lib.sal_attention_decode_split_f16(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(),
+                                                out.data_ptr(), heads, kv_heads, hd, k_cache.shape[0], float(scale),
+                                                workspace.data_ptr(), workspace.numel(), _stream(q))
+        if rc != _lib.SAL_E_UNSUPPORTED:
+            _lib.check(rc, "sal_attention_decode_split_f16")
+            return
     _lib.check(lib.sal_attention_decode_f16(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), pos.data_ptr(),
                                             out.data_ptr(), heads, kv_heads, hd, k_cache.shape[0], float(scale),
                                             _stream(q)), "sal_attention_decode_f16")

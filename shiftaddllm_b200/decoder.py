@@ -124,6 +124,7 @@ class BcqLlamaDecoder:
         self._q32, self._k32, self._v32 = torch.zeros(1, h, **f32), torch.zeros(1, kvh * hd, **f32), torch.zeros(1, kvh * hd, **f32)
         self._o32, self._down32 = torch.zeros(1, h, **f32), torch.zeros(1, h, **f32)
         self._gate32, self._up32 = torch.zeros(1, shape.ffn, **f32), torch.zeros(1, shape.ffn, **f32)
+        self._attn_ws = decode_ops.attention_workspace(shape.heads, hd, self.device) if fused else None
         self.graph = None
 
     # ---- one token ------------------------------------------------------------------------
@@ -185,7 +186,8 @@ class BcqLlamaDecoder:
             _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q, self._k, self._v))
             decode_ops.rope_kv_write(self._q, self._k, self._v, self.cos, self.sin, self.pos, self.k_cache[li],
                                      self.v_cache[li], s.heads, kvh, hd)
-            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale)
+            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale,
+                                        self._attn_ws)
             _group((blk.o_proj,), self._attn, (self._o,))
             decode_ops.residual_rmsnorm(x, self._o, blk.post_norm, hn, x, s.eps)
             _group((blk.gate_proj, blk.up_proj), hn, (self._gate, self._up))
@@ -219,7 +221,8 @@ class BcqLlamaDecoder:
             _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q32, self._k32, self._v32), atomic=True)
             decode_ops.rope_kv_write_f32acc(self._q32, self._k32, self._v32, self._q, self.cos, self.sin, self.pos,
                                             self.k_cache[li], self.v_cache[li], s.heads, kvh, hd)
-            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale)
+            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale,
+                                        self._attn_ws)
             _group((blk.o_proj,), self._attn, (self._o32,), atomic=True)
             decode_ops.residual_rmsnorm_f32acc(x, self._o32, blk.post_norm, hn, x, s.eps)
             _group((blk.gate_proj, blk.up_proj), hn, (self._gate32, self._up32), atomic=True)

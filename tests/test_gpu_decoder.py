@@ -108,6 +108,33 @@ def test_fused_helpers_match_torch():
     assert float((out.float() - ref).abs().max()) < 4e-3
 
 
+@pytest.mark.parametrize("heads,kvh,hd,max_len,pos_v", [(8, 2, 64, 40, 17), (32, 32, 128, 784, 600), (64, 8, 128, 1296, 1100),
+                                                        (4, 4, 32, 16, 0), (16, 2, 128, 300, 299), (8, 4, 256, 64, 33)])
+def test_split_attention_matches_torch(heads, kvh, hd, max_len, pos_v):
+    """Attention split over the cached positions (one CTA per kv head and slice, merged by the last
+    one to finish) against torch, for plain and grouped-query layouts, and run twice on one scratch
+    buffer (the arrival counters must have reset themselves)."""
+    from shiftaddllm_b200 import decode_ops
+
+    g = torch.Generator(device="cuda").manual_seed(heads * 1000 + pos_v)
+    q = torch.randn(heads * hd, device="cuda", generator=g).half()
+    kc = torch.randn(max_len, kvh, hd, device="cuda", generator=g).half()
+    vc = torch.randn(max_len, kvh, hd, device="cuda", generator=g).half()
+    pos = torch.tensor([pos_v], device="cuda")
+    ws = decode_ops.attention_workspace(heads, hd, "cuda")
+    kk = kc[: pos_v + 1].float().repeat_interleave(heads // kvh, dim=1)
+    vv = vc[: pos_v + 1].float().repeat_interleave(heads // kvh, dim=1)
+    sc = torch.einsum("hd,thd->ht", q.view(heads, hd).float(), kk) / math.sqrt(hd)
+    ref = torch.einsum("ht,thd->hd", torch.softmax(sc, -1), vv).reshape(-1)
+    for _ in range(2):
+        out = torch.zeros(heads * hd, dtype=torch.float16, device="cuda")
+        decode_ops.attention_decode(q, kc, vc, pos, out, heads, kvh, hd, 1.0 / math.sqrt(hd), ws)
+        assert float((out.float() - ref).abs().max()) < 4e-3
+    plain = torch.empty_like(out)
+    decode_ops.attention_decode(q, kc, vc, pos, plain, heads, kvh, hd, 1.0 / math.sqrt(hd))
+    assert float((out.float() - plain.float()).abs().max()) < 2e-3
+
+
 def test_accumulator_consuming_helpers():
     """The fp32-accumulator variants give what the fp16 helpers give on the rounded accumulator, and
     leave every accumulator they were handed at zero."""
