@@ -59,6 +59,16 @@ int sal_attention_decode_split_f16(const void *q, const void *k_cache, const voi
                                    int heads, int kv_heads, int hd, int max_len, float scale, void *workspace,
                                    size_t workspace_bytes, void *stream);
 
+/* Rotary step + cache write + split attention in ONE kernel (one launch less per decoder block).  q [heads][hd],
+ * k_new / v_new [kv_heads][hd] are the un-rotated projections of the new token: fp16 (inputs_f32 = 0; q is
+ * left as it is), or fp32 accumulators (inputs_f32 = 1) that are rounded to fp16 on read and cleared.  The
+ * rotated key and the value are stored at position *pos of the caches (nothing is stored if *pos is outside
+ * 0..max_len-1) and attention runs over positions 0..*pos.  Same shape limits, scratch buffer and results as
+ * sal_rope_kv_write_f16 followed by sal_attention_decode_split_f16. */
+int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_f32, const void *cos, const void *sin,
+                              const int64_t *pos, void *k_cache, void *v_cache, void *out, int heads, int kv_heads, int hd,
+                              int max_len, float scale, void *workspace, size_t workspace_bytes, void *stream);
+
 /* out = silu(gate) * up, fp16 vectors of n elements. */
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream);
 

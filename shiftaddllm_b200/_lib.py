@@ -66,6 +66,10 @@ SIGNATURES = {
     "sal_attention_decode_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp]),
     "sal_attention_workspace_bytes": (ctypes.c_size_t, [_i, _i]),
     "sal_attention_decode_split_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp, ctypes.c_size_t, _vp]),
+    "sal_pack_planes_i8": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "sal_repack_lat_to_kernel": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "sal_rope_attention_decode": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp,
+                                       ctypes.c_size_t, _vp]),
     "sal_silu_mul_f16": (_i, [_vp, _vp, _vp, _i, _vp]),
 }
 

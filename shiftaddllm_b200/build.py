@@ -12,8 +12,8 @@ import sys
 
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 REPO_DIR = os.path.dirname(PKG_DIR)
-SRCS = [os.path.join(PKG_DIR, "csrc", "sal_lutgemm.cu"), os.path.join(PKG_DIR, "csrc", "sal_decode_ops.cu")]
-HDRS = [os.path.join(REPO_DIR, "include", "sal_lutgemm.h"), os.path.join(REPO_DIR, "include", "sal_decode_ops.h")]
+SRCS = [os.path.join(PKG_DIR, "csrc", name) for name in ("sal_lutgemm.cu", "sal_decode_ops.cu", "sal_pack.cu")]
+HDRS = [os.path.join(REPO_DIR, "include", name) for name in ("sal_lutgemm.h", "sal_decode_ops.h", "sal_pack.h")]
 LIB = os.path.join(PKG_DIR, "libsal_lutgemm.so")
 
 NVCC_FLAGS = [

@@ -281,12 +281,27 @@ constexpr int ATTN_WARPS = 8;
 
 // STAGE_V: the slice's V rows are fetched together with its K rows and parked in shared memory, so the
 // second pass does not wait for memory again (used when the slice fits).
-template <int G, bool STAGE_V>
-__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const __half *q, const __half *k_cache,
-                                                                          const __half *v_cache, const int64_t *pos_p,
-                                                                          __half *out, float *partial, unsigned *counters,
-                                                                          int kv_heads, int hd, int max_len, float scale,
-                                                                          int nsplit, int slice_cap) {
+// ROPE: the rotary step of the new token is done here instead of by a kernel of its own.  q is the
+// un-rotated query (rotated while it is loaded); the CTA whose slice holds position *pos rotates the new
+// key, writes it and the new value into the caches and then reads them back like any other row.
+// ROPE = 2: q, k_new, v_new are fp32 accumulators, rounded to fp16 on read and cleared afterwards (k, v by
+// the CTA that consumed them; q by the CTA that merges, i.e. after every CTA of the kv head has read it).
+struct RopeArgs {
+    void *k_new, *v_new;       // [kv_heads][hd], fp16 (ROPE 1) or fp32 (ROPE 2)
+    const float *cos_t, *sin_t;  // [max_len][hd / 2]
+};
+template <int ROPE>
+__device__ __forceinline__ float rope_in(const void *p, size_t i) {
+    if (ROPE == 2) return __half2float(__float2half_rn(reinterpret_cast<const float *>(p)[i]));
+    return __half2float(reinterpret_cast<const __half *>(p)[i]);
+}
+
+template <int G, bool STAGE_V, int ROPE>
+__global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const void *q, __half *k_cache, __half *v_cache,
+                                                                          const int64_t *pos_p, __half *out, float *partial,
+                                                                          unsigned *counters, int kv_heads, int hd,
+                                                                          int max_len, float scale, int nsplit,
+                                                                          int slice_cap, RopeArgs ra) {
     extern __shared__ float smem_f[];
     __shared__ float s_m[G], s_l[G];
     __shared__ float s_w[ATTN_MAX_SPLIT][G];
@@ -300,7 +315,9 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
     const int kvh = blockIdx.x, split = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     int64_t pos = *pos_p;
+    const bool pos_ok = pos >= 0 && pos < max_len;
     if (pos >= max_len) pos = max_len - 1;
+    if (pos < 0) pos = 0;
     const int T = (int)pos + 1;
     const int per = (T + nsplit - 1) / nsplit;
     const int t_begin = split * per;
@@ -309,8 +326,39 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
     const int lpr_shift = 31 - __clz(lpr), hd_shift = lpr_shift + 3;
     const int rows = 32 >> lpr_shift;    // positions per warp and load instruction
     const int sub = lane >> lpr_shift, sl = lane & (lpr - 1);
-    for (int i = tid; i < G * hd; i += blockDim.x) qf[i] = __half2float(q[(size_t)kvh * G * hd + i]) * scale;
-    __syncthreads();
+    if (ROPE == 0) {
+        const __half *qh = reinterpret_cast<const __half *>(q);
+        for (int i = tid; i < G * hd; i += blockDim.x) qf[i] = __half2float(qh[(size_t)kvh * G * hd + i]) * scale;
+    } else {
+        const int half = hd >> 1;
+        const float *cs = ra.cos_t + (size_t)pos * half, *sn = ra.sin_t + (size_t)pos * half;
+        for (int i = tid; i < G * half; i += blockDim.x) {
+            const int g = i >> (hd_shift - 1), j = i & (half - 1);
+            const size_t at = ((size_t)kvh * G + g) * hd + j;
+            const float a = rope_in<ROPE>(q, at), b = rope_in<ROPE>(q, at + half);
+            // rounded to fp16 as a separate rotary kernel would have stored it
+            qf[g * hd + j] = __half2float(__float2half_rn(a * cs[j] - b * sn[j])) * scale;
+            qf[g * hd + half + j] = __half2float(__float2half_rn(b * cs[j] + a * sn[j])) * scale;
+        }
+        if (pos_ok && t_begin <= (int)pos && (int)pos < t_begin + n) {   // this CTA's slice ends with the new token
+            __half *krow = k_cache + ((size_t)pos * kv_heads + kvh) * hd, *vrow = v_cache + ((size_t)pos * kv_heads + kvh) * hd;
+            for (int j = tid; j < half; j += blockDim.x) {
+                const size_t at = (size_t)kvh * hd + j;
+                const float a = rope_in<ROPE>(ra.k_new, at), b = rope_in<ROPE>(ra.k_new, at + half);
+                krow[j] = __float2half_rn(a * cs[j] - b * sn[j]);
+                krow[half + j] = __float2half_rn(b * cs[j] + a * sn[j]);
+            }
+            if (ROPE == 2) __syncthreads();   // (CTA-uniform branch) the key is fully read before it is cleared
+            for (int j = tid; j < hd; j += blockDim.x) {
+                vrow[j] = __float2half_rn(rope_in<ROPE>(ra.v_new, (size_t)kvh * hd + j));
+                if (ROPE == 2) {
+                    reinterpret_cast<float *>(ra.k_new)[(size_t)kvh * hd + j] = 0.f;
+                    reinterpret_cast<float *>(ra.v_new)[(size_t)kvh * hd + j] = 0.f;
+                }
+            }
+        }
+    }
+    __syncthreads();   // also orders the cache rows written above before this CTA's reads of them
     const size_t row_stride = (size_t)kv_heads * hd;
     const __half *kbase = k_cache + ((size_t)t_begin * kv_heads + kvh) * hd + sl * 8;
     const __half *vbase = v_cache + ((size_t)t_begin * kv_heads + kvh) * hd + sl * 8;
@@ -496,42 +544,74 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
         }
         out[((size_t)kvh * G + g) * hd + d] = __float2half_rn(acc);
     }
+    if (ROPE == 2) {   // every CTA of this kv head has arrived, hence has read the query accumulators
+        float *q32 = reinterpret_cast<float *>(const_cast<void *>(q));
+        for (int i = tid; i < G * hd; i += blockDim.x) q32[(size_t)kvh * G * hd + i] = 0.f;
+    }
     if (tid == 0) counters[kvh] = 0u;   // ready for the next call
 }
 
 constexpr size_t ATTN_WS_HEADER = 1024;   // arrival counters, one per kv head (<= 256 heads)
 
-template <int G, bool STAGE_V>
+template <int G, bool STAGE_V, int ROPE>
 int launch_attention_variant(size_t smem, const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
                              int kv_heads, int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap,
-                             cudaStream_t stream) {
+                             const RopeArgs &ra, cudaStream_t stream) {
     if (smem + 2048 > 48 * 1024) {   // the kernel's static shared memory counts against the default limit too
         static size_t configured = 0;
         if (configured < smem) {
-            if (cudaFuncSetAttribute(attention_split_kernel<G, STAGE_V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
-                cudaSuccess)
+            if (cudaFuncSetAttribute(attention_split_kernel<G, STAGE_V, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)smem) != cudaSuccess)
                 return SAL_E_LAUNCH;
             configured = smem;
         }
     }
-    return launch_pdl(attention_split_kernel<G, STAGE_V>, dim3(kv_heads, nsplit), dim3(ATTN_WARPS * 32), smem, stream,
-                      reinterpret_cast<const __half *>(q), reinterpret_cast<const __half *>(k_cache),
-                      reinterpret_cast<const __half *>(v_cache), pos, reinterpret_cast<__half *>(out),
+    return launch_pdl(attention_split_kernel<G, STAGE_V, ROPE>, dim3(kv_heads, nsplit), dim3(ATTN_WARPS * 32), smem, stream, q,
+                      reinterpret_cast<__half *>(const_cast<void *>(k_cache)), reinterpret_cast<__half *>(const_cast<void *>(v_cache)),
+                      pos, reinterpret_cast<__half *>(out),
                       reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + ATTN_WS_HEADER),
-                      reinterpret_cast<unsigned *>(workspace), kv_heads, hd, max_len, scale, nsplit, slice_cap);
+                      reinterpret_cast<unsigned *>(workspace), kv_heads, hd, max_len, scale, nsplit, slice_cap, ra);
 }
 
-template <int G>
+template <int G, int ROPE>
 int launch_attention_split(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int kv_heads,
-                           int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap, cudaStream_t stream) {
+                           int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap, const RopeArgs &ra,
+                           cudaStream_t stream) {
     const size_t base = (size_t)(G * hd + G * slice_cap + ATTN_WARPS * G * hd) * sizeof(float);
     const size_t staged = base + (size_t)slice_cap * hd * sizeof(__half);
     if (staged <= 96 * 1024)
-        return launch_attention_variant<G, true>(staged, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace,
-                                                 nsplit, slice_cap, stream);
+        return launch_attention_variant<G, true, ROPE>(staged, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale,
+                                                       workspace, nsplit, slice_cap, ra, stream);
     if (base > 200 * 1024) return SAL_E_UNSUPPORTED;
-    return launch_attention_variant<G, false>(base, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit,
-                                              slice_cap, stream);
+    return launch_attention_variant<G, false, ROPE>(base, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace,
+                                                    nsplit, slice_cap, ra, stream);
+}
+
+template <int ROPE>
+int attention_split_entry(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int heads,
+                          int kv_heads, int hd, int max_len, float scale, void *workspace, size_t workspace_bytes,
+                          const RopeArgs &ra, void *stream) {
+    if (!q || !k_cache || !v_cache || !pos || !out || !workspace) return SAL_E_NULL;
+    if (heads < 1 || kv_heads < 1 || kv_heads > 256 || heads % kv_heads || max_len < 1 || max_len > 65536) return SAL_E_SHAPE;
+    if (hd != 32 && hd != 64 && hd != 128 && hd != 256) return SAL_E_UNSUPPORTED;
+    if (workspace_bytes < ATTN_WS_HEADER + (size_t)heads * ATTN_MAX_SPLIT * (size_t)(hd + 2) * sizeof(float)) return SAL_E_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return SAL_E_ALIGN;
+    const int G = heads / kv_heads;
+    // about three CTAs per SM (they are small), at least ~16 positions per slice at the longest context
+    int nsplit = (444 + kv_heads - 1) / kv_heads;
+    if (nsplit > ATTN_MAX_SPLIT) nsplit = ATTN_MAX_SPLIT;
+    if (G >= 8 && nsplit > ATTN_MAX_SPLIT / 2) nsplit = ATTN_MAX_SPLIT / 2;   // the merge grows with G x slices (measured)
+    if (nsplit > (max_len + 15) / 16) nsplit = (max_len + 15) / 16;
+    if (nsplit < 1) nsplit = 1;
+    const int slice_cap = (max_len + nsplit - 1) / nsplit;
+    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    switch (G) {
+        case 1: return launch_attention_split<1, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
+        case 2: return launch_attention_split<2, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
+        case 4: return launch_attention_split<4, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
+        case 8: return launch_attention_split<8, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
+        default: return SAL_E_UNSUPPORTED;
+    }
 }
 
 }  // namespace
@@ -610,27 +690,19 @@ size_t sal_attention_workspace_bytes(int heads, int hd) {
 int sal_attention_decode_split_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
                                    int heads, int kv_heads, int hd, int max_len, float scale, void *workspace,
                                    size_t workspace_bytes, void *stream) {
-    if (!q || !k_cache || !v_cache || !pos || !out || !workspace) return SAL_E_NULL;
-    if (heads < 1 || kv_heads < 1 || kv_heads > 256 || heads % kv_heads || max_len < 1 || max_len > 65536) return SAL_E_SHAPE;
-    if (hd != 32 && hd != 64 && hd != 128 && hd != 256) return SAL_E_UNSUPPORTED;
-    if (workspace_bytes < sal_attention_workspace_bytes(heads, hd)) return SAL_E_WORKSPACE;
-    if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return SAL_E_ALIGN;
-    const int G = heads / kv_heads;
-    // about three CTAs per SM (they are small), at least ~16 positions per slice at the longest context
-    int nsplit = (444 + kv_heads - 1) / kv_heads;
-    if (nsplit > ATTN_MAX_SPLIT) nsplit = ATTN_MAX_SPLIT;
-    if (G >= 8 && nsplit > ATTN_MAX_SPLIT / 2) nsplit = ATTN_MAX_SPLIT / 2;   // the merge grows with G x slices (measured)
-    if (nsplit > (max_len + 15) / 16) nsplit = (max_len + 15) / 16;
-    if (nsplit < 1) nsplit = 1;
-    const int slice_cap = (max_len + nsplit - 1) / nsplit;
-    cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    switch (G) {
-        case 1: return launch_attention_split<1>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
-        case 2: return launch_attention_split<2>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
-        case 4: return launch_attention_split<4>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
-        case 8: return launch_attention_split<8>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, s);
-        default: return SAL_E_UNSUPPORTED;
-    }
+    return attention_split_entry<0>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace, workspace_bytes,
+                                    RopeArgs{}, stream);
+}
+
+int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_f32, const void *cos, const void *sin,
+                              const int64_t *pos, void *k_cache, void *v_cache, void *out, int heads, int kv_heads, int hd,
+                              int max_len, float scale, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!k_new || !v_new || !cos || !sin) return SAL_E_NULL;
+    const RopeArgs ra = {k_new, v_new, reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin)};
+    return inputs_f32 ? attention_split_entry<2>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace,
+                                                 workspace_bytes, ra, stream)
+                      : attention_split_entry<1>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace,
+                                                 workspace_bytes, ra, stream);
 }
 
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream) {

@@ -68,6 +68,24 @@ def attention_decode(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, scale: 
                                             _stream(q)), "sal_attention_decode_f16")
 
 
+def rope_attention_decode(q, k_new, v_new, cos, sin, pos, k_cache, v_cache, out, heads, kv_heads, hd, scale: float, workspace):
+    """Rotary step of the new token, cache write and split attention in one kernel.  q / k_new / v_new: fp16
+    projections (left untouched) or fp32 accumulators (consumed and cleared).  Returns False — having done
+    nothing — for shapes the split kernel does not take."""
+    lib = _lib.load()
+    f32 = q.dtype == torch.float32
+    if k_new.dtype != q.dtype or v_new.dtype != q.dtype or q.dtype not in (torch.float16, torch.float32):
+        raise RuntimeError("q, k_new and v_new must all be float16 or all float32")
+    rc = lib.sal_rope_attention_decode(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), 1 if f32 else 0, cos.data_ptr(),
+                                       sin.data_ptr(), pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                       heads, kv_heads, hd, k_cache.shape[0], float(scale), workspace.data_ptr(),
+                                       workspace.numel(), _stream(out))
+    if rc == _lib.SAL_E_UNSUPPORTED:
+        return False
+    _lib.check(rc, "sal_rope_attention_decode")
+    return True
+
+
 def silu_mul(gate, up, out):
     lib = _lib.load()
     _lib.check(lib.sal_silu_mul_f16(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _stream(gate)),

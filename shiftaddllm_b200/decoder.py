@@ -125,6 +125,7 @@ class BcqLlamaDecoder:
         self._o32, self._down32 = torch.zeros(1, h, **f32), torch.zeros(1, h, **f32)
         self._gate32, self._up32 = torch.zeros(1, shape.ffn, **f32), torch.zeros(1, shape.ffn, **f32)
         self._attn_ws = decode_ops.attention_workspace(shape.heads, hd, self.device) if fused else None
+        self._rope_fused = True   # rotary step inside the attention kernel (set False to run it as a kernel of its own)
         self.graph = None
 
     # ---- one token ------------------------------------------------------------------------
@@ -184,10 +185,13 @@ class BcqLlamaDecoder:
         for li, blk in enumerate(self.blocks):
             decode_ops.residual_rmsnorm(x, delta, blk.input_norm, hn, x, s.eps)
             _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q, self._k, self._v))
-            decode_ops.rope_kv_write(self._q, self._k, self._v, self.cos, self.sin, self.pos, self.k_cache[li],
-                                     self.v_cache[li], s.heads, kvh, hd)
-            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale,
-                                        self._attn_ws)
+            if not (self._rope_fused and decode_ops.rope_attention_decode(
+                    self._q, self._k, self._v, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li], self._attn,
+                    s.heads, kvh, hd, scale, self._attn_ws)):
+                decode_ops.rope_kv_write(self._q, self._k, self._v, self.cos, self.sin, self.pos, self.k_cache[li],
+                                         self.v_cache[li], s.heads, kvh, hd)
+                decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd,
+                                            scale, self._attn_ws)
             _group((blk.o_proj,), self._attn, (self._o,))
             decode_ops.residual_rmsnorm(x, self._o, blk.post_norm, hn, x, s.eps)
             _group((blk.gate_proj, blk.up_proj), hn, (self._gate, self._up))
@@ -219,10 +223,13 @@ class BcqLlamaDecoder:
             pend = (self._gate32, self._up32) if li > 0 else (None, None)
             decode_ops.residual_rmsnorm_f32acc(x, delta, blk.input_norm, hn, x, s.eps, *pend)
             _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q32, self._k32, self._v32), atomic=True)
-            decode_ops.rope_kv_write_f32acc(self._q32, self._k32, self._v32, self._q, self.cos, self.sin, self.pos,
-                                            self.k_cache[li], self.v_cache[li], s.heads, kvh, hd)
-            decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd, scale,
-                                        self._attn_ws)
+            if not (self._rope_fused and decode_ops.rope_attention_decode(
+                    self._q32, self._k32, self._v32, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li],
+                    self._attn, s.heads, kvh, hd, scale, self._attn_ws)):
+                decode_ops.rope_kv_write_f32acc(self._q32, self._k32, self._v32, self._q, self.cos, self.sin, self.pos,
+                                                self.k_cache[li], self.v_cache[li], s.heads, kvh, hd)
+                decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd,
+                                            scale, self._attn_ws)
             _group((blk.o_proj,), self._attn, (self._o32,), atomic=True)
             decode_ops.residual_rmsnorm_f32acc(x, self._o32, blk.post_norm, hn, x, s.eps)
             _group((blk.gate_proj, blk.up_proj), hn, (self._gate32, self._up32), atomic=True)

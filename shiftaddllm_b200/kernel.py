@@ -15,7 +15,7 @@ import torch.nn as nn
 from .quant import LutLinear, make_lut
 
 __all__ = [
-    "pack_binaryWeight", "unpack_weight", "unpack_to_fake_binaryWeight", "convert_weight", "to_kernel_layout",
+    "pack_binaryWeight", "pack_to_kernel_layout", "unpack_weight", "unpack_to_fake_binaryWeight", "convert_weight", "to_kernel_layout",
     "find_layers", "load_shiftaddllm_weight", "load_shiftaddllm_weight_with_kernel",
 ]
 
@@ -42,15 +42,44 @@ def _unpack_along(words: torch.Tensor, dim: int) -> torch.Tensor:
     return bits.flatten(-2).movedim(-1, dim)
 
 
+def _pack_planes_cuda(bWeight: torch.Tensor, kernel_layout: bool) -> torch.Tensor:
+    """CUDA tensors: one pass of ``sal_pack_planes_i8`` over the +-1 planes (the step the reference
+    leaves on the CPU, model/opt.py:287)."""
+    from . import _lib
+
+    lib = _lib.load()
+    r, ng, gsz, q = bWeight.shape
+    c = ng * gsz
+    signs = bWeight.to(torch.int8).contiguous()
+    out = torch.empty((c // 32, q, r) if kernel_layout else (r, c // 32, q), dtype=torch.int32, device=bWeight.device)
+    bad = torch.zeros(1, dtype=torch.int32, device=bWeight.device)
+    with torch.cuda.device(bWeight.device):
+        _lib.check(lib.sal_pack_planes_i8(signs.data_ptr(), out.data_ptr(), r, c, q, 1 if kernel_layout else 0, bad.data_ptr(),
+                                          torch.cuda.current_stream(bWeight.device).cuda_stream), "sal_pack_planes_i8")
+    if int(bad.item()):
+        raise ValueError("BinaryWeight should be 1 or -1, but got other values")
+    return out
+
+
+def pack_to_kernel_layout(bWeight: torch.Tensor) -> torch.Tensor:
+    """``[N, n_groups, group_size, wbit]`` of +-1 -> int32 ``[K/32, wbit, N]``: ``pack_binaryWeight``
+    followed by ``to_kernel_layout``, as one kernel when the tensor is on a GPU."""
+    if bWeight.is_cuda and bWeight.dim() == 4 and (bWeight.shape[1] * bWeight.shape[2]) % 32 == 0 and bWeight.shape[3] <= 8:
+        return _pack_planes_cuda(bWeight, True)
+    return to_kernel_layout(pack_binaryWeight(bWeight))
+
+
 def pack_binaryWeight(bWeight: torch.Tensor) -> torch.Tensor:
     """``[R, n_groups, group_size, wbit]`` of +-1 -> int32 ``[R, C/32, wbit]``,
     C = n_groups*group_size, bit t of word j = (element 32*j+t == +1).
-    Same contract as lut_gemm/kernel.py:9-23."""
+    Same contract as lut_gemm/kernel.py:9-23.  CUDA tensors are packed by a CUDA kernel."""
     if bWeight.dim() != 4:
         raise ValueError(f"BinaryWeight shape should be [N, n_groups, group_size, wbit], got {tuple(bWeight.shape)}")
     r, ng, gsz, q = bWeight.shape
     if (ng * gsz) % 32:
         raise ValueError("n_groups*group_size must be a multiple of 32")
+    if bWeight.is_cuda and q <= 8 and (ng * gsz) // 32 <= 65535:
+        return _pack_planes_cuda(bWeight, False)
     pos = bWeight == 1
     if not bool((pos | (bWeight == -1)).all()):
         raise ValueError("BinaryWeight should be 1 or -1, but got other values")
@@ -103,6 +132,16 @@ def convert_weight(BinaryWeight: torch.Tensor, Alpha: torch.Tensor):
     k_in, w, q = BinaryWeight.shape
     if k_in % 32:
         raise ValueError("in_features must be a multiple of 32")
+    if BinaryWeight.is_cuda and BinaryWeight.dtype == torch.int32 and q <= 8:
+        from . import _lib
+
+        src = BinaryWeight.contiguous()
+        out = torch.empty((k_in // 32, q, w * 32), dtype=torch.int32, device=src.device)
+        with torch.cuda.device(src.device):
+            _lib.check(_lib.load().sal_repack_lat_to_kernel(src.data_ptr(), out.data_ptr(), k_in, w * 32, q,
+                                                           torch.cuda.current_stream(src.device).cuda_stream),
+                       "sal_repack_lat_to_kernel")
+        return out, Alpha.transpose(1, 2).float().contiguous()
     bits = _unpack_along(BinaryWeight, 1)  # [K_in, N_out, q]
     repacked = _pack_along(bits, 0)        # [K_in/32, N_out, q]
     return repacked.permute(0, 2, 1).contiguous(), Alpha.transpose(1, 2).float().contiguous()

@@ -13,7 +13,7 @@ REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def declared_functions():
     names = set()
-    for header in ("sal_lutgemm.h", "sal_decode_ops.h"):
+    for header in ("sal_lutgemm.h", "sal_decode_ops.h", "sal_pack.h"):
         text = open(os.path.join(REPO, "include", header)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
         names |= set(re.findall(r"\b(sal_[a-z0-9_]+)\s*\(", text))
@@ -39,7 +39,7 @@ def test_version_and_strings(lib):
 def test_planner_without_gpu(lib):
     info = _lib.SalPlanInfo()
     assert lib.sal_plan_shift_scale(1, 4096, 4096, 3, 32, ctypes.byref(info)) == 0
-    assert info.tiled == 1 and info.ranges * info.splits == info.ctas and info.stages >= 2
+    assert info.tiled == 1 and 1 <= info.ctas <= info.ranges * info.splits and info.stages >= 2
     assert info.smem_bytes <= 115712            # two CTAs must fit one SM
     assert lib.sal_plan_shift_scale(1, 4096, 4096, 3, 128, ctypes.byref(info)) == 0   # g = 32
     assert info.tiled == 0

@@ -135,6 +135,43 @@ def test_split_attention_matches_torch(heads, kvh, hd, max_len, pos_v):
     assert float((out.float() - plain.float()).abs().max()) < 2e-3
 
 
+@pytest.mark.parametrize("heads,kvh,hd,max_len,pos_v,f32", [(8, 2, 64, 40, 17, False), (32, 32, 128, 200, 150, True),
+                                                            (64, 8, 128, 300, 0, True), (8, 8, 32, 64, 63, False)])
+def test_rope_attention_fused_equals_two_kernels(heads, kvh, hd, max_len, pos_v, f32):
+    """Rotary step + cache write + attention in one kernel against the two separate helpers:
+    same cache contents and the same output; fp32 accumulator inputs are consumed and cleared."""
+    from shiftaddllm_b200 import decode_ops
+
+    g = torch.Generator(device="cuda").manual_seed(pos_v + heads)
+    q = torch.randn(heads * hd, device="cuda", generator=g)
+    k = torch.randn(kvh * hd, device="cuda", generator=g)
+    v = torch.randn(kvh * hd, device="cuda", generator=g)
+    kc = torch.randn(max_len, kvh, hd, device="cuda", generator=g).half()
+    vc = torch.randn(max_len, kvh, hd, device="cuda", generator=g).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+    ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([pos_v], device="cuda")
+    ws = decode_ops.attention_workspace(heads, hd, "cuda")
+    scale = 1.0 / math.sqrt(hd)
+    # two kernels
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    q_ref, out_ref = q.half(), torch.empty(heads * hd, dtype=torch.float16, device="cuda")
+    decode_ops.rope_kv_write(q_ref, k.half(), v.half(), cos, sin, pos, kc_ref, vc_ref, heads, kvh, hd)
+    decode_ops.attention_decode(q_ref, kc_ref, vc_ref, pos, out_ref, heads, kvh, hd, scale, ws)
+    # one kernel
+    qi, ki, vi = (q.clone(), k.clone(), v.clone()) if f32 else (q.half(), k.half(), v.half())
+    out = torch.empty_like(out_ref)
+    assert decode_ops.rope_attention_decode(qi, ki, vi, cos, sin, pos, kc, vc, out, heads, kvh, hd, scale, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+    assert float((out.float() - out_ref.float()).abs().max()) < 1e-3
+    if f32:
+        assert not qi.any() and not ki.any() and not vi.any()
+    else:
+        assert torch.equal(qi, q.half())          # fp16 inputs are left as they were
+
+
 def test_accumulator_consuming_helpers():
     """The fp32-accumulator variants give what the fp16 helpers give on the rounded accumulator, and
     leave every accumulator they were handed at zero."""
