@@ -1654,7 +1654,10 @@ int sal_lutgemv_shift_scale(const void *bw, const void *alpha, const void *bias,
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     if (!(flags & SAL_FORCE_GENERIC) && tiled_eligible(bw, alpha, bias, x, y, M, K, N, q, num_groups)) {
         sal_problem sp = {bw, alpha, bias, x, y, M, K, N, q, num_groups};
-        return run_tiled_group(&sp, 1, flags, workspace, workspace_bytes, s, nullptr);
+        rc = run_tiled_group(&sp, 1, flags, workspace, workspace_bytes, s, nullptr);
+        // a scratch buffer that is too small for this shape (or more row pairs x column ranges than it has
+        // arrival counters) is not an error for the reference-style call: the generic kernel takes it
+        if (rc != SAL_E_WORKSPACE || (flags & (SAL_OUT_F32_ATOMIC | SAL_SWIGLU_F32))) return rc;
     }
     GenericParams p = {};
     p.bw = reinterpret_cast<const uint32_t *>(bw);
@@ -1716,8 +1719,11 @@ static int block_entry(int kind, const void *bw, const void *alpha, const void *
     if (!(flags & SAL_FORCE_GENERIC) && block_tiled_eligible(bw, alpha, x, M, K, N, q, num_groups, kind, num_apot)) {
         sal_problem sp = {bw, alpha, bias, x, y, M, K, N, q, /*num_groups (unused in block mode)*/ 1};
         const BlockAlpha blk = {kind, num_groups, N / num_groups, num_apot};
-        return run_tiled_group(&sp, 1, flags & (SAL_ACCUMULATE | SAL_PDL), workspace, workspace_bytes,
-                               reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr, &blk);
+        rc = run_tiled_group(&sp, 1, flags & (SAL_ACCUMULATE | SAL_PDL), workspace, workspace_bytes,
+                             reinterpret_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr, &blk);
+        // many rows x many column ranges can outgrow the arrival counters of the scratch buffer (one
+        // counter per row and range in this mode): the generic kernel takes those
+        if (rc != SAL_E_WORKSPACE) return rc;
     }
     return run_generic(kind, p, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream));
 }
