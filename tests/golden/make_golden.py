@@ -27,7 +27,7 @@ import torch
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of an unmodified checkout of GATECH-EIC/ShiftAddLLM")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(os.path.abspath(__file__)), "reference_vectors.npz"))
     args = ap.parse_args()
 

@@ -342,6 +342,34 @@ def test_block_modes_on_the_tiled_kernel(k, n, gs, q, m):
     assert_status_clean()
 
 
+def test_limits_of_the_interface():
+    """The documented extremes: 8 bit planes (generic kernel), 64 activation rows in one call, the
+    smallest legal K, and the first values past the limits (error codes, nothing launched)."""
+    lib = _lib.load()
+    layer = synth.make_layer(256, 64, 8, 128, bias=True)                       # q = SAL_MAX_Q
+    assert o.max_rel_err(run_mode_a(layer), ref_mode_a(layer)) <= TOL
+    layer = synth.make_layer(512, 256, 2, 128, M=64, packed_draw=True)          # M = SAL_MAX_M
+    assert o.max_rel_err(run_mode_a(layer), ref_mode_a(layer)) <= TOL
+    layer = synth.make_layer(32, 8, 3, 32)                                      # one packed word per column
+    assert o.max_rel_err(run_mode_a(layer), ref_mode_a(layer)) <= TOL
+    bw, al, x = dev(layer.bWeight), dev(layer.alpha), dev(layer.x)
+    y = torch.zeros(1, 8, dtype=torch.float16, device="cuda")
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def call(m, k, n, q, groups):
+        return lib.sal_lutgemv_shift_scale(bw.data_ptr(), al.data_ptr(), None, x.data_ptr(), y.data_ptr(), m, k, n, q, groups, 0,
+                                           None, 0, stream)
+
+    assert call(65, 32, 8, 3, 1) == _lib.SAL_E_SHAPE        # too many rows
+    assert call(1, 32, 8, 9, 1) == _lib.SAL_E_SHAPE         # too many planes
+    assert call(1, 48, 8, 3, 1) == _lib.SAL_E_SHAPE         # K not a multiple of 32
+    assert call(0, 32, 8, 3, 1) == _lib.SAL_E_SHAPE         # empty batch
+    assert call(1, 32, 0, 3, 1) == _lib.SAL_E_SHAPE         # no output columns
+    assert call(1, 32, 8, 3, 3) == _lib.SAL_E_SHAPE         # groups do not divide K
+    torch.cuda.synchronize()
+    assert not y.any()                                       # nothing ran
+
+
 def test_bad_calls_raise():
     layer = synth.make_layer(256, 64, 3, 128)
     bw, al, x = dev(layer.bWeight), dev(layer.alpha), dev(layer.x)
