@@ -281,6 +281,124 @@ class BcqLlamaDecoder:
         return torch.cat(out)
 
 
+class BcqLlamaBatchDecoder:
+    """Greedy decoder for `batch` sequences that advance in lock step (one shared position counter, as in a
+    benchmark where all prompts have the same length).  The linear layers run as ONE small-batch LUT product
+    per group (M = batch: the weights are streamed once for all sequences); the steps between them are plain
+    torch ops, which at batch > 1 amortise their launch cost over the batch.  Weights are those of a
+    `BcqLlamaDecoder` (pass it as `like` to share them instead of drawing new ones)."""
+
+    def __init__(self, shape: LlamaShape, wbits: int = 3, group_size: int = 128, max_len: int = 640, batch: int = 16,
+                 device="cuda", seed: int = 0, like: "BcqLlamaDecoder | None" = None):
+        if not 1 <= batch <= 64:
+            raise ValueError("batch must be 1..64 (rows of one small-batch LUT product)")
+        self.shape, self.max_len, self.batch = shape, max_len, batch
+        self.device = torch.device(device)
+        if like is None:
+            like = BcqLlamaDecoder(shape, wbits, group_size, max_len=8, device=device, seed=seed, fused=False)
+        self.embed, self.lm_head, self.final_norm, self.blocks = like.embed, like.lm_head, like.final_norm, like.blocks
+        hd, kvh, h, b = shape.head_dim, shape.kv_heads, shape.hidden, batch
+        self.k_cache = torch.zeros(shape.layers, b, max_len, kvh, hd, dtype=torch.float16, device=self.device)
+        self.v_cache = torch.zeros_like(self.k_cache)
+        inv = 1.0 / (shape.rope_theta ** (torch.arange(0, hd, 2, device=self.device).float() / hd))
+        ang = torch.arange(max_len, device=self.device).float()[:, None] * inv[None, :]
+        self.cos, self.sin = ang.cos(), ang.sin()
+        self.positions = torch.arange(max_len, device=self.device)
+        self.token = torch.zeros(b, dtype=torch.long, device=self.device)
+        self.pos = torch.zeros(1, dtype=torch.long, device=self.device)
+        self.logits = torch.zeros(b, shape.vocab, dtype=torch.float32, device=self.device)
+        f16 = dict(dtype=torch.float16, device=self.device)
+        self._q, self._k, self._v = torch.empty(b, h, **f16), torch.empty(b, kvh * hd, **f16), torch.empty(b, kvh * hd, **f16)
+        self._o, self._down = torch.empty(b, h, **f16), torch.empty(b, h, **f16)
+        self._gate, self._up = torch.empty(b, shape.ffn, **f16), torch.empty(b, shape.ffn, **f16)
+        self.graph = None
+
+    def _rope(self, t, heads):
+        hd, b = self.shape.head_dim, self.batch
+        cos = self.cos.index_select(0, self.pos)        # [1, hd/2], the same position for every sequence
+        sin = self.sin.index_select(0, self.pos)
+        t = t.view(b, heads, 2, hd // 2).float()
+        a, c = t[:, :, 0, :], t[:, :, 1, :]
+        return torch.stack((a * cos - c * sin, c * cos + a * sin), dim=2).view(b, heads, hd).half()
+
+    def step(self):
+        s, b = self.shape, self.batch
+        hd, kvh, rep = s.head_dim, s.kv_heads, s.heads // s.kv_heads
+        x = self.embed.index_select(0, self.token)                      # [b, hidden]
+        mask = (self.positions > self.pos).view(1, 1, 1, -1)
+        for li, blk in enumerate(self.blocks):
+            hn = F.rms_norm(x, (s.hidden,), blk.input_norm, s.eps)
+            _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q, self._k, self._v))
+            qh, kh = self._rope(self._q, s.heads), self._rope(self._k, kvh)
+            self.k_cache[li].index_copy_(1, self.pos, kh.view(b, 1, kvh, hd))
+            self.v_cache[li].index_copy_(1, self.pos, self._v.view(b, 1, kvh, hd))
+            keys = self.k_cache[li].permute(0, 2, 3, 1)                 # [b, kvh, hd, T]
+            vals = self.v_cache[li].permute(0, 2, 1, 3)                 # [b, kvh, T, hd]
+            scores = torch.matmul(qh.view(b, kvh, rep, hd), keys).float() * (1.0 / math.sqrt(hd))
+            scores = scores.masked_fill(mask, float("-inf"))
+            attn = torch.matmul(torch.softmax(scores, dim=-1).half(), vals).reshape(b, s.hidden)
+            _group((blk.o_proj,), attn, (self._o,))
+            x = x + self._o
+            hn = F.rms_norm(x, (s.hidden,), blk.post_norm, s.eps)
+            _group((blk.gate_proj, blk.up_proj), hn, (self._gate, self._up))
+            _group((blk.down_proj,), self._gate, (self._down,), x_mul=self._up)   # SiLU(gate)*up formed in the table build
+            x = x + self._down
+        hn = F.rms_norm(x, (s.hidden,), self.final_norm, s.eps)
+        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float())
+        self.token.copy_(self.logits.argmax(dim=-1))
+        self.pos.add_(1)
+
+    capture = BcqLlamaDecoder.capture
+    generate_step = step
+
+    def reset(self):
+        self.token.zero_()
+        self.pos.zero_()
+        self.k_cache.zero_()
+        self.v_cache.zero_()
+
+    def feed(self, token_rows):
+        """Teacher-forced pass over prompts of equal length: `token_rows` [length][batch] token ids."""
+        run = self.graph.replay if self.graph is not None else self.step
+        for row in token_rows:
+            self.token.copy_(torch.as_tensor(row, dtype=torch.long, device=self.device))
+            run()
+
+    def generate(self, n):
+        run = self.graph.replay if self.graph is not None else self.step
+        out = []
+        for _ in range(n):
+            run()
+            out.append(self.token.clone())
+        return torch.stack(out)                                          # [n, batch]
+
+
+def benchmark_batch(model: BcqLlamaBatchDecoder, prompt_len: int, new_tokens: int, warmup: int = 5, seed: int = 0):
+    """Aggregate tokens/s of `model.batch` sequences decoded in lock step (wall clock over the new
+    tokens, one device sync at the end), after prompts of `prompt_len` uniform random ids."""
+    dev = model.device
+    gen = torch.Generator().manual_seed(seed)
+    prompts = torch.randint(0, model.shape.vocab, (prompt_len, model.batch), generator=gen)
+    if model.graph is None:
+        model.capture()
+    model.reset()
+    model.feed(prompts)
+    torch.cuda.synchronize(dev)
+    state = (model.token.clone(), model.pos.clone())
+    for _ in range(warmup):
+        model.graph.replay()
+    model.token.copy_(state[0])
+    model.pos.copy_(state[1])
+    torch.cuda.synchronize(dev)
+    t0 = time.perf_counter()
+    for _ in range(new_tokens):
+        model.graph.replay()
+    torch.cuda.synchronize(dev)
+    wall = time.perf_counter() - t0
+    return {"tokens_per_s": model.batch * new_tokens / wall, "ms_per_step": 1e3 * wall / new_tokens, "batch": model.batch,
+            "prompt_len": prompt_len, "new_tokens": new_tokens}
+
+
 def benchmark(model: BcqLlamaDecoder, prompt_len: int, new_tokens: int, warmup: int = 10, seed: int = 0):
     """tokens/s over `new_tokens` greedy decode steps after a `prompt_len`-token prompt of uniform
     random ids (wall clock, one device sync at the end), plus the reference-style median of
@@ -325,8 +443,15 @@ def main():
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--no-fused", action="store_true", help="plain torch ops between the GEMVs")
     ap.add_argument("--atomic", action="store_true", help="GEMVs accumulate into fp32 buffers with atomics (no split-K tail)")
+    ap.add_argument("--batch", type=int, default=1, help="sequences decoded in lock step (small-batch LUT products)")
     args = ap.parse_args()
     shape = SHAPES[args.model]
+    if args.batch > 1:
+        model = BcqLlamaBatchDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16, batch=args.batch)
+        res = benchmark_batch(model, args.prompt, args.new)
+        res.update({"model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompts"})
+        print(json.dumps(res))
+        return
     model = BcqLlamaDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16, fused=not args.no_fused,
                             atomic=args.atomic)
     res = benchmark(model, args.prompt, args.new)

@@ -260,6 +260,29 @@ def test_atomic_mode_tracks_the_deterministic_mode():
     assert torch.equal(b.generate(6).cpu(), ta)
 
 
+def test_batch_decoder_matches_single_sequences():
+    """Three sequences decoded in lock step (small-batch LUT products, M = 3) give the logits of
+    the same three sequences decoded one at a time with the same weights."""
+    from shiftaddllm_b200.decoder import BcqLlamaBatchDecoder
+
+    single = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=32, seed=2, fused=False)
+    batch = BcqLlamaBatchDecoder(SHAPES["tiny"], max_len=32, batch=3, like=single)
+    prompts = torch.tensor([[5, 17, 400], [9, 2, 77], [123, 8, 31], [44, 44, 6]])          # [length][batch]
+    batch.reset()
+    batch.feed(prompts.tolist())
+    torch.cuda.synchronize()
+    for col in range(3):
+        single.reset()
+        single.feed(prompts[:, col].tolist())
+        torch.cuda.synchronize()
+        a, b = batch.logits[col].cpu(), single.logits.cpu()
+        assert float((a - b).abs().max()) <= 2e-2 * float(b.abs().max())
+        assert int(batch.token[col]) == int(single.token)
+    batch.capture()
+    toks = batch.generate(3)
+    assert toks.shape == (3, 3)
+
+
 def test_benchmark_runs():
     model = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=96, seed=3)
     res = benchmark(model, prompt_len=16, new_tokens=8, warmup=2)
