@@ -340,7 +340,8 @@ def decode_tokens_per_s(workload, device):
     """The other half of the metric: greedy batch-1 decode of a whole decoder of the workload's
     architecture (random init, every linear a synthetic BCQ layer): 128 new tokens after a
     512-token prompt (1024 for the 70B shape), the step replayed as one CUDA graph.  Reported for
-    fixed-order fp16 GEMV outputs and for the opt-in fp32 atomic accumulation."""
+    fixed-order fp16 GEMV outputs and for the opt-in fp32 atomic accumulation; for the 7B shape also 16
+    sequences decoded in lock step (64 new tokens each) on the small-batch kernel."""
     from shiftaddllm_b200 import decoder
 
     prompt = 512 if workload == "llama2-7b" else 1024
@@ -352,6 +353,13 @@ def decode_tokens_per_s(workload, device):
             r = decoder.benchmark(model, prompt, 128)
             res[name] = {"tokens_per_s": round(r["tokens_per_s"], 1), "ms_per_token": round(r["ms_per_token"], 4),
                          "median_ms_per_token_synced": round(r["median_ms_per_token_synced"], 4)}
+        if workload == "llama2-7b":
+            # 16 sequences in lock step: the linears run the small-batch (M = 16) LUT kernel
+            batch = decoder.BcqLlamaBatchDecoder(decoder.SHAPES[workload], Q, G, max_len=prompt + 64 + 16, batch=16, device=device,
+                                                 like=model)
+            r = decoder.benchmark_batch(batch, prompt, 64)
+            res["batch16_fp16_outputs"] = {"tokens_per_s": round(r["tokens_per_s"], 1), "ms_per_step": round(r["ms_per_step"], 3),
+                                           "new_tokens_per_sequence": 64}
     res["workload"] = (f"{workload}-shaped decoder, BCQ {Q}-bit g128 linears, fp16 lm_head, batch 1, {prompt}-token prompt of "
                        "uniform random ids, 128 greedy tokens, one CUDA graph per token")
     return res

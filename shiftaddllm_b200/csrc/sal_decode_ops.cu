@@ -302,7 +302,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
                                                                           unsigned *counters, int kv_heads, int hd,
                                                                           int max_len, float scale, int nsplit,
                                                                           int slice_cap, RopeArgs ra) {
-    extern __shared__ float smem_f[];
+    extern __shared__ __align__(16) float smem_f[];
     __shared__ float s_m[G], s_l[G];
     __shared__ float s_w[ATTN_MAX_SPLIT][G];
     __shared__ int s_is_last;
@@ -603,7 +603,9 @@ int attention_split_entry(const void *q, const void *k_cache, const void *v_cach
     if (G >= 8 && nsplit > ATTN_MAX_SPLIT / 2) nsplit = ATTN_MAX_SPLIT / 2;   // the merge grows with G x slices (measured)
     if (nsplit > (max_len + 15) / 16) nsplit = (max_len + 15) / 16;
     if (nsplit < 1) nsplit = 1;
-    const int slice_cap = (max_len + nsplit - 1) / nsplit;
+    // capacity of a slice, rounded up to a multiple of 4: the staged V rows behind the G x slice_cap scores in
+    // shared memory are written with 16-byte stores
+    const int slice_cap = ((max_len + nsplit - 1) / nsplit + 3) & ~3;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     switch (G) {
         case 1: return launch_attention_split<1, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);

@@ -109,7 +109,8 @@ def test_fused_helpers_match_torch():
 
 
 @pytest.mark.parametrize("heads,kvh,hd,max_len,pos_v", [(8, 2, 64, 40, 17), (32, 32, 128, 784, 600), (64, 8, 128, 1296, 1100),
-                                                        (4, 4, 32, 16, 0), (16, 2, 128, 300, 299), (8, 4, 256, 64, 33)])
+                                                        (4, 4, 32, 16, 0), (16, 2, 128, 300, 299), (8, 4, 256, 64, 33),
+                                                        (8, 8, 128, 601, 600), (4, 4, 64, 203, 77)])
 def test_split_attention_matches_torch(heads, kvh, hd, max_len, pos_v):
     """Attention split over the cached positions (one CTA per kv head and slice, merged by the last
     one to finish) against torch, for plain and grouped-query layouts, and run twice on one scratch
