@@ -21,7 +21,7 @@ extern "C" {
 
 /* t = x (+ delta if delta != NULL); if x_out != NULL, x_out = t (the updated residual stream);
  * out = t * rsqrt(mean(t^2) + eps) * weight.  fp16 tensors of n elements, fp32 arithmetic.
- * x_out may alias x. */
+ * x_out may alias x.  1 <= n <= 12000. */
 int sal_residual_rmsnorm_f16(const void *x, const void *delta, const void *weight, void *out, void *x_out, int n,
                              float eps, void *stream);
 

@@ -39,11 +39,61 @@ __device__ __forceinline__ float block_reduce(float v, float *red, bool is_max) 
     return r;
 }
 
+// Fast path of the norm kernels: at most 8 elements per thread, n a multiple of 8, 16-byte aligned operands.
+__device__ __forceinline__ bool fast_rows_ok(int n, const void *a, const void *b, const void *c, const void *d, const void *e) {
+    const uintptr_t bits = reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(c) |
+                           reinterpret_cast<uintptr_t>(d) | reinterpret_cast<uintptr_t>(e);
+    return (n % 8 == 0) && n <= 8 * (int)blockDim.x && (bits & 15) == 0;
+}
+// out[0..8) = t * inv * w (fp16), x_out[0..8) = t (fp16), one 16-byte store each
+__device__ __forceinline__ void store_normed(const float (&t)[8], const uint4 &wv, float inv, __half *out, __half *x_out) {
+    const __half *wh = reinterpret_cast<const __half *>(&wv);
+    uint4 ov, xv;
+    __half *oh = reinterpret_cast<__half *>(&ov), *xh = reinterpret_cast<__half *>(&xv);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        oh[k] = __float2half_rn(t[k] * inv * __half2float(wh[k]));
+        xh[k] = __float2half_rn(t[k]);
+    }
+    *reinterpret_cast<uint4 *>(out) = ov;
+    if (x_out) *reinterpret_cast<uint4 *>(x_out) = xv;
+}
+
 __global__ void __launch_bounds__(1024) residual_rmsnorm_kernel(const __half *x, const __half *delta, const __half *w,
                                                                 __half *out, __half *x_out, int n, float eps) {
     __shared__ float red[32];
     extern __shared__ float tbuf[];  // n floats
     pdl_prologue();
+    if (fast_rows_ok(n, x, delta, w, out, x_out)) {
+        // n <= 8 x threads, everything 16-byte aligned: a thread keeps its 8 elements in registers, every
+        // operand is fetched with one 16-byte load and all loads are in flight together
+        const int i = threadIdx.x * 8;
+        const bool mine = i < n;
+        float t[8];
+        uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+        if (mine) {
+            const uint4 xv = *reinterpret_cast<const uint4 *>(x + i);
+            wv = *reinterpret_cast<const uint4 *>(w + i);
+            uint4 dv = make_uint4(0u, 0u, 0u, 0u);
+            if (delta) dv = *reinterpret_cast<const uint4 *>(delta + i);
+            const __half *xh = reinterpret_cast<const __half *>(&xv), *dh = reinterpret_cast<const __half *>(&dv);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                t[k] = __half2float(xh[k]);
+                if (delta) t[k] = __half2float(__float2half_rn(t[k] + __half2float(dh[k])));
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = 0.f;
+        }
+        float ssq = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ssq += t[k] * t[k];
+        ssq = block_reduce(ssq, red, false);
+        const float inv_f = rsqrtf(ssq / (float)n + eps);
+        if (mine) store_normed(t, wv, inv_f, out + i, x_out ? x_out + i : nullptr);
+        return;
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float t = __half2float(x[i]);
@@ -69,6 +119,48 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half
     __shared__ float red[32];
     extern __shared__ float tbuf[];  // n floats
     pdl_prologue();
+    if (blockIdx.x > 0) {
+        // CTAs 1.. only clear the extra accumulators (hundreds of KB for an FFN-wide pair): nothing here depends
+        // on the norm, so it runs beside it instead of in front of it
+        const int stride = (gridDim.x - 1) * blockDim.x, first = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
+        for (int i = first; i < zero_a_n; i += stride) zero_a[i] = 0.f;
+        for (int i = first; i < zero_b_n; i += stride) zero_b[i] = 0.f;
+        return;
+    }
+    if (fast_rows_ok(n, x, delta, w, out, x_out)) {
+        const int i = threadIdx.x * 8;
+        const bool mine = i < n;
+        float t[8];
+        uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+        if (mine) {
+            const uint4 xv = *reinterpret_cast<const uint4 *>(x + i);
+            wv = *reinterpret_cast<const uint4 *>(w + i);
+            float4 d0 = make_float4(0.f, 0.f, 0.f, 0.f), d1 = d0;
+            if (delta) {
+                d0 = *reinterpret_cast<const float4 *>(delta + i);
+                d1 = *reinterpret_cast<const float4 *>(delta + i + 4);
+                *reinterpret_cast<float4 *>(delta + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+                *reinterpret_cast<float4 *>(delta + i + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            const float df[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+            const __half *xh = reinterpret_cast<const __half *>(&xv);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                t[k] = __half2float(xh[k]);
+                if (delta) t[k] = __half2float(__float2half_rn(t[k] + __half2float(__float2half_rn(df[k]))));
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) t[k] = 0.f;
+        }
+        float ssq = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) ssq += t[k] * t[k];
+        ssq = block_reduce(ssq, red, false);
+        const float inv_f = rsqrtf(ssq / (float)n + eps);
+        if (mine) store_normed(t, wv, inv_f, out + i, x_out ? x_out + i : nullptr);
+        return;
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float t = __half2float(x[i]);
@@ -79,8 +171,6 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half
         tbuf[i] = t;
         ss += t * t;
     }
-    for (int i = threadIdx.x; i < zero_a_n; i += blockDim.x) zero_a[i] = 0.f;
-    for (int i = threadIdx.x; i < zero_b_n; i += blockDim.x) zero_b[i] = 0.f;
     ss = block_reduce(ss, red, false);
     const float inv = rsqrtf(ss / (float)n + eps);
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -623,7 +713,7 @@ extern "C" {
 int sal_residual_rmsnorm_f16(const void *x, const void *delta, const void *weight, void *out, void *x_out, int n, float eps,
                              void *stream) {
     if (!x || !weight || !out) return SAL_E_NULL;
-    if (n < 1 || n > 32768) return SAL_E_SHAPE;
+    if (n < 1 || n > 12000 /* the row is staged in shared memory, 48 KB with the reduction scratch */) return SAL_E_SHAPE;
     const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
     return launch_pdl(residual_rmsnorm_kernel, dim3(1), dim3(threads), (size_t)n * sizeof(float), stream,
                       reinterpret_cast<const __half *>(x), reinterpret_cast<const __half *>(delta),
@@ -645,9 +735,12 @@ int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos
 int sal_residual_rmsnorm_f32acc(const void *x, void *delta_f32, const void *weight, void *out, void *x_out, int n, float eps,
                                 void *zero_a, int zero_a_n, void *zero_b, int zero_b_n, void *stream) {
     if (!x || !weight || !out) return SAL_E_NULL;
-    if (n < 1 || n > 12288 /* the row is staged in 48 KB of shared memory */ || zero_a_n < 0 || zero_b_n < 0 || (zero_a_n && !zero_a) || (zero_b_n && !zero_b)) return SAL_E_SHAPE;
+    if (n < 1 || n > 12000 /* the row is staged in shared memory, 48 KB with the reduction scratch */ || zero_a_n < 0 || zero_b_n < 0 || (zero_a_n && !zero_a) || (zero_b_n && !zero_b)) return SAL_E_SHAPE;
     const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
-    return launch_pdl(residual_rmsnorm_f32_kernel, dim3(1), dim3(threads), (size_t)n * sizeof(float), stream,
+    // one CTA for the norm, plus one per 16 K extra accumulator words to clear (at most 32)
+    int zero_ctas = (zero_a_n + zero_b_n + 16383) / 16384;
+    if (zero_ctas > 32) zero_ctas = 32;
+    return launch_pdl(residual_rmsnorm_f32_kernel, dim3(1 + zero_ctas), dim3(threads), (size_t)n * sizeof(float), stream,
                       reinterpret_cast<const __half *>(x), reinterpret_cast<float *>(delta_f32),
                       reinterpret_cast<const __half *>(weight), reinterpret_cast<__half *>(out), reinterpret_cast<__half *>(x_out),
                       n, eps, reinterpret_cast<float *>(zero_a), zero_a_n, reinterpret_cast<float *>(zero_b), zero_b_n);

@@ -173,6 +173,27 @@ def test_rope_attention_fused_equals_two_kernels(heads, kvh, hd, max_len, pos_v,
         assert torch.equal(qi, q.half())          # fp16 inputs are left as they were
 
 
+@pytest.mark.parametrize("n", [40, 1000, 4096, 8192, 12000])
+def test_rmsnorm_helpers_all_sizes(n):
+    """Register fast path (n % 8 == 0, n <= 8192) and the general path of both norm kernels against torch."""
+    from shiftaddllm_b200 import decode_ops
+
+    g = torch.Generator(device="cuda").manual_seed(n)
+    x = torch.randn(1, n, device="cuda", generator=g).half()
+    d = torch.randn(1, n, device="cuda", generator=g).half()
+    w = (1 + 0.1 * torch.randn(n, device="cuda", generator=g)).half()
+    t = x + d
+    ref = t.float() * torch.rsqrt(t.float().pow(2).mean() + 1e-5) * w.float()
+    out, xo = torch.empty_like(x), torch.empty_like(x)
+    decode_ops.residual_rmsnorm(x, d, w, out, xo, 1e-5)
+    assert torch.equal(xo, t) and float((out.float() - ref).abs().max()) < 6e-3
+    d32, za = d.float(), torch.ones(40000, device="cuda")
+    out2, x_inplace = torch.empty_like(x), x.clone()
+    decode_ops.residual_rmsnorm_f32acc(x_inplace, d32, w, out2, x_inplace, 1e-5, za, None)
+    assert torch.equal(x_inplace, t) and torch.equal(out2, out)
+    assert not d32.any() and not za.any()
+
+
 def test_accumulator_consuming_helpers():
     """The fp32-accumulator variants give what the fp16 helpers give on the rounded accumulator, and
     leave every accumulator they were handed at zero."""
