@@ -113,13 +113,20 @@ int sal_lutgemv_shift_scale(const void *bw, const void *alpha, const void *bias,
  *  - The first call on each device looks up the array's device address and, for shapes that use
  *    the tiled kernel, runs a one-off probe that synchronises the stream: make that first call
  *    outside any stream capture.
- *  - Every call uses the SAME array and first clears its status word and counters on `stream`.
+ *  - Every call uses the SAME array and first clears its arrival counters on `stream` (the status
+ *    word is left for sal_static_status).
  *    Calls that can overlap on the GPU (different streams, or one stream with concurrent graph
  *    branches) race on it and give wrong results: keep them ordered, or use the workspace entry.
  *  - It calls no cudaMalloc/cudaFree and no allocating library routine.
  */
 int sal_lutgemv_shift_scale_static(const void *bw, const void *alpha, const void *bias, const void *x, void *y,
                                    int M, int K, int N, int q, int num_groups, unsigned flags, void *stream);
+
+/* Companion of sal_lutgemv_shift_scale_static (no counterpart in the reference either): reads back
+ * (synchronously, on `stream`) and clears the device-side status word of the built-in scratch of the
+ * current device — SAL_OK, SAL_E_TIMEOUT or SAL_E_UNSUPPORTED.  The word is sticky: calls of the
+ * static entry leave it alone, so a status recorded by an earlier call is still there. */
+int sal_static_status(void *stream);
 
 /*
  * One alpha per (group, column), halved for each successive plane, plus an
@@ -178,6 +185,10 @@ typedef struct sal_problem {
 
 int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags,
                         void *workspace, size_t workspace_bytes, void *stream);
+/* All problems of a group share M and the activation form (x_mul or not).  Their plane counts q may
+ * differ (layers of one block quantised to different widths, as the reference's per-layer mixed
+ * precision does: model/opt.py:83-88,104-107): the group is then issued as one kernel per distinct q,
+ * in the order the widths first appear. */
 
 /*
  * Grouped launch with the all-gather of the output slices FUSED into the kernel (column-parallel
@@ -205,6 +216,27 @@ int sal_lutgemv_grouped_exchange(const sal_problem *problems, int count, unsigne
                                  void *workspace, size_t workspace_bytes, const sal_exchange *exchange,
                                  int *writers_out, void *stream);
 
+/*
+ * Prepared launches: sal_lutgemv_grouped / sal_lutgemv_grouped_exchange split in two.  Preparing validates
+ * the problems, plans the work split and encodes the tensor-map descriptors of the packed planes (driver
+ * calls) ONCE; launching then only binds a scratch buffer and enqueues the kernel(s).  This is the form a
+ * decoder uses: the same launches every token.  No counterpart in the reference (its launchers recompute
+ * their grid on every call, mv_fp16_bias.hpp:581-645).
+ *  - The pointers inside `problems` (and `exchange`, may be NULL) are remembered, not the memory behind
+ *    them: the tensors must stay where they are while the handle is used.
+ *  - A handle belongs to the device that was current when it was prepared.
+ *  - `workspace` as for sal_lutgemv_grouped, at least sal_prepared_workspace_bytes() bytes.
+ *  - `slot`: counter slot of a fused-exchange launch (ignored without exchange; < 0 keeps the slot given
+ *    at preparation).  sal_prepared_writers: arrivals this rank contributes per launch (0 without exchange).
+ */
+typedef struct sal_prepared sal_prepared;
+int sal_prepare_grouped(const sal_problem *problems, int count, unsigned flags, const sal_exchange *exchange,
+                        sal_prepared **out);
+size_t sal_prepared_workspace_bytes(const sal_prepared *prepared);
+int sal_prepared_writers(const sal_prepared *prepared);
+int sal_launch_prepared(const sal_prepared *prepared, void *workspace, size_t workspace_bytes, int slot, void *stream);
+void sal_destroy_prepared(sal_prepared *prepared);
+
 /* Enqueues a one-thread kernel that waits (bounded, about one second; SAL_E_TIMEOUT is recorded
  * in the workspace status word if it gives up) until counter `slot` of this rank's flag array
  * reaches `expected`, then clears it.  `workspace` may be NULL (no status reporting). */
@@ -222,7 +254,9 @@ typedef struct sal_plan_info {
 } sal_plan_info;
 int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_info *out);
 
-/* Measurement hook, process-wide, not for production use.  Keys: "stages" caps the
+#ifdef SAL_MEASURE
+/* Measurement hook, process-wide; exists only in libraries built with -DSAL_MEASURE (the product
+ * build has neither this symbol nor the switches it sets).  Keys: "stages" caps the
  * depth of the shared-memory ring of the tiled kernel (0 = as deep as fits);
  * "budget_pct" scales the number of SMs the planner sizes its grid for
  * (100 = one CTA per SM, 200 = two, 0 = automatic); "full_sm" lets a CTA use a
@@ -232,6 +266,7 @@ int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_in
  * (results are then meaningless; used to time the parts); "force_per" and
  * "force_splits" override the planner's column tiles per CTA and K splits. */
 int sal_debug_set(const char *key, int value);
+#endif
 
 #ifdef __cplusplus
 }

@@ -11,7 +11,8 @@ import ctypes
 import os
 
 _PKG_DIR = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_PKG_DIR, "libsal_lutgemm.so")
+# SAL_LUTGEMM_LIBRARY names another build of the same library (e.g. one compiled with -DSAL_MEASURE)
+LIB_PATH = os.environ.get("SAL_LUTGEMM_LIBRARY") or os.path.join(_PKG_DIR, "libsal_lutgemm.so")
 
 SAL_OK = 0
 SAL_E_NULL, SAL_E_SHAPE, SAL_E_ALIGN, SAL_E_WORKSPACE = -1, -2, -3, -4
@@ -48,6 +49,7 @@ SIGNATURES = {
     "sal_workspace_status": (_i, [_vp, _vp]),
     "sal_lutgemv_shift_scale": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemv_shift_scale_static": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp]),
+    "sal_static_status": (_i, [_vp]),
     "sal_lutgemv_compute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemm_block": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
     "sal_lutgemm_block_shift": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _u, _vp, _sz, _vp]),
@@ -56,8 +58,12 @@ SIGNATURES = {
     "sal_lutgemv_grouped_exchange": (_i, [ctypes.POINTER(SalProblem), _i, _u, _vp, _sz, ctypes.POINTER(SalExchange),
                                           ctypes.POINTER(_i), _vp]),
     "sal_exchange_wait": (_i, [_vp, _i, _u, _vp, _vp]),
+    "sal_prepare_grouped": (_i, [ctypes.POINTER(SalProblem), _i, _u, ctypes.POINTER(SalExchange), ctypes.POINTER(_vp)]),
+    "sal_prepared_workspace_bytes": (_sz, [_vp]),
+    "sal_prepared_writers": (_i, [_vp]),
+    "sal_launch_prepared": (_i, [_vp, _vp, _sz, _i, _vp]),
+    "sal_destroy_prepared": (None, [_vp]),
     "sal_plan_shift_scale": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(SalPlanInfo)]),
-    "sal_debug_set": (_i, [ctypes.c_char_p, _i]),
     # include/sal_decode_ops.h
     "sal_residual_rmsnorm_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _vp]),
     "sal_rope_kv_write_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
@@ -89,6 +95,9 @@ def load() -> ctypes.CDLL:
             fn = getattr(lib, name)
             fn.restype = res
             fn.argtypes = args
+        if hasattr(lib, "sal_debug_set"):   # present only in measurement builds (-DSAL_MEASURE)
+            lib.sal_debug_set.restype = _i
+            lib.sal_debug_set.argtypes = [ctypes.c_char_p, _i]
         _lib = lib
     return _lib
 

@@ -648,12 +648,15 @@ int launch_attention_variant(size_t smem, const void *q, const void *k_cache, co
                              int kv_heads, int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap,
                              const RopeArgs &ra, cudaStream_t stream) {
     if (smem + 2048 > 48 * 1024) {   // the kernel's static shared memory counts against the default limit too
-        static size_t configured = 0;
-        if (configured < smem) {
+        // the attribute belongs to the (function, device) pair: remember it per device ordinal
+        static size_t configured[64];
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SAL_E_DEVICE;
+        if (configured[dev] < smem) {
             if (cudaFuncSetAttribute(attention_split_kernel<G, STAGE_V, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem) != cudaSuccess)
                 return SAL_E_LAUNCH;
-            configured = smem;
+            configured[dev] = smem;
         }
     }
     return launch_pdl(attention_split_kernel<G, STAGE_V, ROPE>, dim3(kv_heads, nsplit), dim3(ATTN_WARPS * 32), smem, stream, q,
@@ -765,11 +768,13 @@ int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_c
         return SAL_E_SHAPE;
     const size_t smem = (size_t)(hd + max_len + 32 * hd) * sizeof(float);
     if (smem > 48 * 1024) {
-        static bool configured = false;
-        if (!configured) {
+        static bool configured[64];   // per device ordinal: the attribute is not shared between devices
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SAL_E_DEVICE;
+        if (!configured[dev]) {
             if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024) != cudaSuccess)
                 return SAL_E_LAUNCH;
-            configured = true;
+            configured[dev] = true;
         }
     }
     return launch_pdl(attention_decode_kernel, dim3(heads), dim3(1024), smem, stream, reinterpret_cast<const __half *>(q),

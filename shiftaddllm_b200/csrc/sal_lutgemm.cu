@@ -34,6 +34,7 @@
 #include <cuda.h>
 #include <cuda_fp16.h>
 #include <mutex>
+#include <new>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -105,11 +106,19 @@ struct TileParams {
     int count;
     int stages;
     int accumulate;
-    int ablate;  // measurement only: bit0 skip alpha loads, bit1 skip table builds, bit2 skip lookups;
-                 // block mode: bit3 skip the multiplier decode + stores, bit4 skip the per-tile barrier
+    int ablate;  // measurement builds (-DSAL_MEASURE) only: bit0 skip alpha loads, bit1 skip table builds, bit2 skip
+                 // lookups; block mode: bit3 skip the multiplier decode + stores, bit4 skip the per-tile barrier
     int *status;
     ExchangeParams ex;
 };
+
+// Parts of the kernel can be switched off to time the others; only in measurement builds, so that
+// the product's hot loop carries no such test and its results cannot be made meaningless.
+#ifdef SAL_MEASURE
+#define SAL_ABLATED(P, bits) (((P).ablate & (bits)) != 0)
+#else
+#define SAL_ABLATED(P, bits) false
+#endif
 
 // ------------------------------------------------------------------------------------------
 // PTX helpers
@@ -503,7 +512,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         }
     };
     __half a_next[2][Q];
-    if (!BLK && kb_begin < kb_end && !(P.ablate & 1)) load_alpha(kb_begin, t_first, a_next);  // constants: legal before the dependency wait
+    if (!BLK && kb_begin < kb_end && !SAL_ABLATED(P, 1)) load_alpha(kb_begin, t_first, a_next);  // constants: legal before the dependency wait
     else {
 #pragma unroll
         for (int b = 0; b < Q; ++b) a_next[0][b] = a_next[1][b] = __float2half(0.f);
@@ -615,7 +624,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     auto process_block = [&](int kb, auto par_tag) {
         constexpr int PAR = BLK ? 0 : decltype(par_tag)::value;
         if constexpr (BLK) consumer_barrier(NCW * 32);  // one set of tables: the previous K block must be finished by all
-        if (!(P.ablate & 2))
+        if (!SAL_ABLATED(P, 2))
         {
             const size_t ko = (size_t)kb * KB_FEATS;
             if (SWIGLU == 2) {   // fp32 operands: same element offsets, twice the bytes (pointers are carried as __half*)
@@ -650,12 +659,12 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                     for (int i = 0; i < NVI; ++i)
 #pragma unroll
                         for (int k = 0; k < NVW; ++k) raw_cur[i][k] = raw_next[i][k];
-                    if (kb_n < kb_end && !(P.ablate & 1)) load_block_alpha(kb_n, more_sub ? sub + 1 : 0, raw_next);
+                    if (kb_n < kb_end && !SAL_ABLATED(P, 1)) load_block_alpha(kb_n, more_sub ? sub + 1 : 0, raw_next);
                     // Safe without a second barrier: whoever writes buffer `mbuf` again has passed the barrier of
                     // the tile in between, which every warp reaches only after its reads of this tile.
-                    if (!(P.ablate & 8)) store_block_mult(raw_cur, mbuf);
-                    if (!(P.ablate & 16)) consumer_barrier(NCW * 32);
-                } else if (kb_n < kb_end && !(P.ablate & 1)) {
+                    if (!SAL_ABLATED(P, 8)) store_block_mult(raw_cur, mbuf);
+                    if (!SAL_ABLATED(P, 16)) consumer_barrier(NCW * 32);
+                } else if (kb_n < kb_end && !SAL_ABLATED(P, 1)) {
                     load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
                 }
             }
@@ -664,7 +673,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             float a_sub[ROWS];
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) a_sub[r] = 0.f;
-            if (!(P.ablate & 4))
+            if (!SAL_ABLATED(P, 4))
 #pragma unroll
             for (int hp = 0; hp < 2; ++hp) {
                 float part[ROWS][Q], part2[ROWS][Q];
@@ -1405,40 +1414,56 @@ bool block_tiled_eligible(const void *bw, const void *alpha, const void *x, int 
     return aligned(bw, 16) && aligned(x, 16) && aligned(alpha, 2);
 }
 
-int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void *workspace, size_t ws_bytes,
-                    cudaStream_t stream, sal_plan_info *info_only, const sal_exchange *ex = nullptr, int *writers_out = nullptr,
-                    const BlockAlpha *blk = nullptr) {
+// A grouped launch of the tiled kernel, planned and marshalled but not yet bound to a scratch buffer: the
+// kernel parameters (problems, work split, one encoded tensor map per problem), the launch geometry and, per
+// problem, where its arrival counters and partial sums go inside whatever scratch buffer a launch is given.
+struct BuiltLaunch {
+    TileParams P;
+    int q, ctas, rows, row_groups, swiglu, smem, writers, M;
+    bool atomic_out;
+    unsigned flags;
+    int counter_off[SAL_MAX_GROUP];  // first arrival counter of the problem, -1 = the problem is not split along K
+    size_t n_off[SAL_MAX_GROUP];     // columns of the problems before it (offset of its partial sums, in columns)
+    size_t ws_need;                  // bytes of scratch a launch needs (0 = none)
+};
+
+// Plans and marshals one grouped launch (all problems share q, M and the activation form).  `allow_split`: a
+// scratch buffer will be there at launch time, so K may be split.  `encode`: also encode the tensor maps (needs a
+// CUDA context; false for the geometry-only query).
+int build_tiled_group(const sal_problem *problems, int count, unsigned flags, bool allow_split, bool encode, const sal_exchange *ex,
+                      const BlockAlpha *blk, BuiltLaunch *out) {
     DeviceInfo *dev = nullptr;
-    if (!info_only) {
+    if (encode) {
         int rc = device_info(&dev);
         if (rc != SAL_OK) return rc;
     }
     const int sms = dev ? dev->sms : 148;
     const int optin = dev ? dev->smem_optin : 232448;
-    const int q = problems[0].q;
-    int smem = 0;
+    BuiltLaunch &L = *out;
+    L = BuiltLaunch{};
+    L.q = problems[0].q;
+    L.flags = flags;
     // Activation rows: M = 1 runs the fp32-table kernel; 2 <= M <= 64 runs the half2-table variant,
     // one pair of rows per grid.y (all problems of a launch must agree on M).
-    const int M = problems[0].M;
-    const int rows = (M > 1 && !blk) ? 2 : 1;
-    const int row_groups = (M + rows - 1) / rows;
+    const int M = L.M = problems[0].M;
+    L.rows = (M > 1 && !blk) ? 2 : 1;
+    L.row_groups = (M + L.rows - 1) / L.rows;
     const int ncw = 8;   // consumer warps per CTA (a 16-warp, one-CTA-per-SM shape was measured and is not faster)
     // all problems of a launch must agree on the activation form
-    const bool atomic_out = (flags & SAL_OUT_F32_ATOMIC) != 0;
-    const int swiglu = problems[0].x_mul == nullptr ? 0 : ((flags & SAL_SWIGLU_F32) ? 2 : 1);
-    if ((atomic_out || swiglu == 2) && (M != 1 || ex)) return SAL_E_UNSUPPORTED;
-    if (blk && (atomic_out || swiglu || ex || count != 1)) return SAL_E_UNSUPPORTED;
+    L.atomic_out = (flags & SAL_OUT_F32_ATOMIC) != 0;
+    L.swiglu = problems[0].x_mul == nullptr ? 0 : ((flags & SAL_SWIGLU_F32) ? 2 : 1);
+    if ((L.atomic_out || L.swiglu == 2) && (M != 1 || ex)) return SAL_E_UNSUPPORTED;
+    if (blk && (L.atomic_out || L.swiglu || ex || count != 1)) return SAL_E_UNSUPPORTED;
     const int cw = ncw * 32;
     const int ctas_per_sm = ncw > 8 ? 1 : 2;
-    const int stages = choose_stages(q, ncw, optin, &smem);
+    const int stages = choose_stages(L.q, ncw, optin, &L.smem);
     if (stages == 0) return SAL_E_UNSUPPORTED;
 
-    TileParams P = {};
+    TileParams &P = L.P;
     P.count = count;
     P.stages = stages;
     P.accumulate = (flags & SAL_ACCUMULATE) ? 1 : 0;
     P.ablate = g_ablate;
-    P.status = workspace ? reinterpret_cast<int *>(workspace) : nullptr;
     if (ex) {
         if (ex->world < 2 || ex->world > SAL_MAX_PEERS || ex->rank < 0 || ex->rank >= ex->world || ex->slot < 0 || M != 1 ||
             !ex->gather_offsets)
@@ -1452,15 +1477,13 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
             P.ex.flags[t] = reinterpret_cast<unsigned *>(ex->peer_flags[t]);
         }
     }
-    int writers = 0;
 
     // every CTA of the launch gets about the same amount of work, whatever problem it belongs to
-    const bool have_ws = workspace != nullptr && ws_bytes >= WS_PARTIAL_OFFSET;
     const int pct = g_budget_pct > 0 ? g_budget_pct : 100 * ctas_per_sm;
-    int slots = (int)(sms * (pct / 100.0) / row_groups);   // row groups share the SMs
+    int slots = (int)(sms * (pct / 100.0) / L.row_groups);   // row groups share the SMs
     if (slots < 4 * count) slots = 4 * count;
     Plan plans[SAL_MAX_GROUP];
-    plan_group(problems, count, slots, have_ws || atomic_out, cw, plans);
+    plan_group(problems, count, slots, allow_split || L.atomic_out, cw, plans);
     int cta = 0;
     int counter_off = 0;
     size_t n_off = 0;
@@ -1492,56 +1515,116 @@ int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void
         tp.splits_last = pl.splits_last;
         tp.cta_begin = cta;
         tp.gather_off = ex ? (long long)ex->gather_offsets[i] : 0;
-        writers += pl.ranges;  // one CTA per column range stores final outputs
-        if (!info_only) {
+        L.writers += pl.ranges;  // one CTA per column range stores final outputs
+        if (encode) {
             const int erc = encode_weight_map(&P.tmap[i], sp.bw, sp.K, sp.N, sp.q);
             if (erc != SAL_OK) return erc;
         }
-        if ((pl.splits > 1 || pl.splits_last > 1) && !atomic_out) {
-            if (counter_off + pl.ranges * row_groups > WS_MAX_COUNTERS) return SAL_E_WORKSPACE;
-            const size_t need = WS_PARTIAL_OFFSET + (n_off + (size_t)sp.N) * (size_t)M * MAX_SPLIT * sizeof(float);
-            if (!info_only && need > ws_bytes) return SAL_E_WORKSPACE;
-            tp.counters = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(workspace) + WS_HEADER_BYTES) + counter_off;
-            tp.partials = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + WS_PARTIAL_OFFSET) + n_off * (size_t)M * MAX_SPLIT;
-            counter_off += pl.ranges * row_groups;
+        L.counter_off[i] = -1;
+        L.n_off[i] = n_off;
+        if ((pl.splits > 1 || pl.splits_last > 1) && !L.atomic_out) {
+            if (counter_off + pl.ranges * L.row_groups > WS_MAX_COUNTERS) return SAL_E_WORKSPACE;
+            L.ws_need = WS_PARTIAL_OFFSET + (n_off + (size_t)sp.N) * (size_t)M * MAX_SPLIT * sizeof(float);
+            L.counter_off[i] = counter_off;
+            counter_off += pl.ranges * L.row_groups;
         }
         n_off += (size_t)sp.N;
         cta += pl.ctas;
     }
-    if (writers_out) *writers_out = writers;
-    if (info_only) {
-        info_only->tiled = 1;
-        info_only->ctas = cta;
-        info_only->ranges = P.p[0].ranges;
-        info_only->splits = P.p[0].splits;
-        info_only->stages = stages;
-        info_only->smem_bytes = smem;
-        return SAL_OK;
+    L.ctas = cta;
+    return SAL_OK;
+}
+
+// Binds a built launch to a scratch buffer (and, for the fused exchange, to a counter slot) and enqueues it.
+int launch_built(const BuiltLaunch &L, void *workspace, size_t ws_bytes, int slot, cudaStream_t stream) {
+    DeviceInfo *dev = nullptr;
+    int rc = device_info(&dev);
+    if (rc != SAL_OK) return rc;
+    if (L.ws_need > 0 && (workspace == nullptr || ws_bytes < L.ws_need)) return SAL_E_WORKSPACE;
+    TileParams P = L.P;
+    P.status = workspace ? reinterpret_cast<int *>(workspace) : nullptr;
+    if (slot >= 0) P.ex.slot = slot;
+    for (int i = 0; i < P.count; ++i) {
+        if (L.counter_off[i] < 0) continue;
+        P.p[i].counters = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(workspace) + WS_HEADER_BYTES) + L.counter_off[i];
+        P.p[i].partials = reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + WS_PARTIAL_OFFSET) + L.n_off[i] * (size_t)L.M * MAX_SPLIT;
     }
     // The first call on a device that has a workspace probes where dynamic shared memory
     // starts (one tiny kernel on `stream`, read back synchronously); it must therefore not be
     // made under stream capture.  Until probed, the variant without baked-in addresses runs.
     if (dev->smem_base == 0 && workspace != nullptr) {
-        uint32_t *slot = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(workspace) + 64);
+        uint32_t *probe = reinterpret_cast<uint32_t *>(reinterpret_cast<char *>(workspace) + 64);
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
         cudaStreamIsCapturing(stream, &cap);
         if (cap == cudaStreamCaptureStatusNone) {
-            smem_base_probe_kernel<<<1, 32, 256, stream>>>(slot);
+            smem_base_probe_kernel<<<1, 32, 256, stream>>>(probe);
             uint32_t base = 0;
-            if (cuda_ok(cudaMemcpyAsync(&base, slot, 4, cudaMemcpyDeviceToHost, stream)) &&
+            if (cuda_ok(cudaMemcpyAsync(&base, probe, 4, cudaMemcpyDeviceToHost, stream)) &&
                 cuda_ok(cudaStreamSynchronize(stream)))
                 dev->smem_base = base ? (int)base : -1;
         }
     }
     const bool abs_ok = dev->smem_base == (int)SMEM_DYNAMIC_BASE;
     cudaError_t e;
-    switch (q) {
-        case 1: e = launch_tiled<1>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
-        case 2: e = launch_tiled<2>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
-        case 3: e = launch_tiled<3>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
-        default: e = launch_tiled<4>(P, cta, rows, row_groups, swiglu, atomic_out, smem, flags, abs_ok, stream); break;
+    switch (L.q) {
+        case 1: e = launch_tiled<1>(P, L.ctas, L.rows, L.row_groups, L.swiglu, L.atomic_out, L.smem, L.flags, abs_ok, stream); break;
+        case 2: e = launch_tiled<2>(P, L.ctas, L.rows, L.row_groups, L.swiglu, L.atomic_out, L.smem, L.flags, abs_ok, stream); break;
+        case 3: e = launch_tiled<3>(P, L.ctas, L.rows, L.row_groups, L.swiglu, L.atomic_out, L.smem, L.flags, abs_ok, stream); break;
+        default: e = launch_tiled<4>(P, L.ctas, L.rows, L.row_groups, L.swiglu, L.atomic_out, L.smem, L.flags, abs_ok, stream); break;
     }
     return cuda_ok(e) ? SAL_OK : SAL_E_LAUNCH;
+}
+
+int run_tiled_group(const sal_problem *problems, int count, unsigned flags, void *workspace, size_t ws_bytes,
+                    cudaStream_t stream, sal_plan_info *info_only, const sal_exchange *ex = nullptr, int *writers_out = nullptr,
+                    const BlockAlpha *blk = nullptr) {
+    BuiltLaunch L;
+    const bool have_ws = workspace != nullptr && ws_bytes >= WS_PARTIAL_OFFSET;
+    int rc = build_tiled_group(problems, count, flags, have_ws, info_only == nullptr, ex, blk, &L);
+    if (rc != SAL_OK) return rc;
+    if (writers_out) *writers_out = L.writers;
+    if (info_only) {
+        info_only->tiled = 1;
+        info_only->ctas = L.ctas;
+        info_only->ranges = L.P.p[0].ranges;
+        info_only->splits = L.P.p[0].splits;
+        info_only->stages = L.P.stages;
+        info_only->smem_bytes = L.smem;
+        return SAL_OK;
+    }
+    return launch_built(L, workspace, ws_bytes, -1, stream);
+}
+
+// Problems of one grouped call sorted into classes of equal plane count q (each class is one kernel launch),
+// keeping the caller's order inside a class.  Returns the number of classes.
+int split_by_q(const sal_problem *problems, int count, sal_problem (*classes)[SAL_MAX_GROUP], int *sizes, int (*index)[SAL_MAX_GROUP]) {
+    int nclass = 0;
+    for (int i = 0; i < count; ++i) {
+        int c = 0;
+        while (c < nclass && classes[c][0].q != problems[i].q) ++c;
+        if (c == nclass) sizes[nclass++] = 0;
+        if (index) index[c][sizes[c]] = i;
+        classes[c][sizes[c]++] = problems[i];
+    }
+    return nclass;
+}
+
+int validate_grouped(const sal_problem *problems, int count, bool exchange) {
+    if (!problems) return SAL_E_NULL;
+    if (count < 1 || count > SAL_MAX_GROUP) return SAL_E_SHAPE;
+    for (int i = 0; i < count; ++i) {
+        const sal_problem &sp = problems[i];
+        int rc = validate_common(sp.bw, sp.alpha, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q);
+        if (rc != SAL_OK) return rc;
+        if (sp.num_groups <= 0 || sp.K % sp.num_groups != 0) return SAL_E_SHAPE;
+        if (sp.M != problems[0].M) return SAL_E_UNSUPPORTED;
+        if (exchange && (sp.M != 1 || sp.x_mul != nullptr)) return SAL_E_UNSUPPORTED;
+        if (sp.x_mul && !aligned(sp.x_mul, 16)) return SAL_E_ALIGN;
+        if ((sp.x_mul != nullptr) != (problems[0].x_mul != nullptr)) return SAL_E_UNSUPPORTED;
+        if (!tiled_eligible(sp.bw, sp.alpha, sp.bias, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q, sp.num_groups))
+            return SAL_E_UNSUPPORTED;
+    }
+    return SAL_OK;
 }
 
 }  // namespace
@@ -1593,6 +1676,7 @@ int sal_workspace_status(void *workspace, void *stream) {
     return st;
 }
 
+#ifdef SAL_MEASURE
 int sal_debug_set(const char *key, int value) {
     if (!key) return SAL_E_NULL;
     const auto eq = [&](const char *k) {
@@ -1618,6 +1702,7 @@ int sal_debug_set(const char *key, int value) {
     }
     return SAL_OK;
 }
+#endif  // SAL_MEASURE
 
 int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_info *out) {
     if (!out) return SAL_E_NULL;
@@ -1747,45 +1832,112 @@ int sal_lutgemm_block_shift_int8(const void *bw, const void *alpha_i8, const voi
 
 int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags, void *workspace,
                         size_t workspace_bytes, void *stream) {
-    if (!problems) return SAL_E_NULL;
-    if (count < 1 || count > SAL_MAX_GROUP) return SAL_E_SHAPE;
-    for (int i = 0; i < count; ++i) {
-        const sal_problem &sp = problems[i];
-        int rc = validate_common(sp.bw, sp.alpha, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q);
-        if (rc != SAL_OK) return rc;
-        if (sp.num_groups <= 0 || sp.K % sp.num_groups != 0) return SAL_E_SHAPE;
-        if (sp.q != problems[0].q || sp.M != problems[0].M) return SAL_E_UNSUPPORTED;
-        if (sp.x_mul && !aligned(sp.x_mul, 16)) return SAL_E_ALIGN;
-        if ((sp.x_mul != nullptr) != (problems[0].x_mul != nullptr)) return SAL_E_UNSUPPORTED;
-        if (!tiled_eligible(sp.bw, sp.alpha, sp.bias, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q, sp.num_groups))
-            return SAL_E_UNSUPPORTED;
-    }
-    DeviceInfo *dev = nullptr;
-    int rc = device_info(&dev);
+    int rc = validate_grouped(problems, count, false);
     if (rc != SAL_OK) return rc;
-    return run_tiled_group(problems, count, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream),
-                           nullptr);
+    DeviceInfo *dev = nullptr;
+    rc = device_info(&dev);
+    if (rc != SAL_OK) return rc;
+    // one kernel launch per plane count (a group of layers quantised to different widths: mixed precision)
+    sal_problem classes[SAL_MAX_GROUP][SAL_MAX_GROUP];
+    int sizes[SAL_MAX_GROUP];
+    const int nclass = split_by_q(problems, count, classes, sizes, nullptr);
+    for (int c = 0; c < nclass; ++c) {
+        rc = run_tiled_group(classes[c], sizes[c], flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream), nullptr);
+        if (rc != SAL_OK) return rc;
+    }
+    return SAL_OK;
 }
 
 int sal_lutgemv_grouped_exchange(const sal_problem *problems, int count, unsigned flags, void *workspace,
                                  size_t workspace_bytes, const sal_exchange *exchange, int *writers_out, void *stream) {
-    if (!problems || !exchange) return SAL_E_NULL;
-    if (count < 1 || count > SAL_MAX_GROUP) return SAL_E_SHAPE;
-    for (int i = 0; i < count; ++i) {
-        const sal_problem &sp = problems[i];
-        int rc = validate_common(sp.bw, sp.alpha, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q);
-        if (rc != SAL_OK) return rc;
-        if (sp.num_groups <= 0 || sp.K % sp.num_groups != 0) return SAL_E_SHAPE;
-        if (sp.q != problems[0].q || sp.M != 1 || sp.x_mul != nullptr) return SAL_E_UNSUPPORTED;
-        if (!tiled_eligible(sp.bw, sp.alpha, sp.bias, sp.x, sp.y, sp.M, sp.K, sp.N, sp.q, sp.num_groups))
-            return SAL_E_UNSUPPORTED;
-    }
-    DeviceInfo *dev = nullptr;
-    int rc = device_info(&dev);
+    if (!exchange) return SAL_E_NULL;
+    int rc = validate_grouped(problems, count, true);
     if (rc != SAL_OK) return rc;
-    return run_tiled_group(problems, count, flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream),
-                           nullptr, exchange, writers_out);
+    if (!exchange->gather_offsets) return SAL_E_NULL;
+    DeviceInfo *dev = nullptr;
+    rc = device_info(&dev);
+    if (rc != SAL_OK) return rc;
+    sal_problem classes[SAL_MAX_GROUP][SAL_MAX_GROUP];
+    int sizes[SAL_MAX_GROUP], index[SAL_MAX_GROUP][SAL_MAX_GROUP];
+    const int nclass = split_by_q(problems, count, classes, sizes, index);
+    int writers = 0;
+    for (int c = 0; c < nclass; ++c) {
+        long long offs[SAL_MAX_GROUP];
+        for (int i = 0; i < sizes[c]; ++i) offs[i] = exchange->gather_offsets[index[c][i]];
+        sal_exchange ex = *exchange;
+        ex.gather_offsets = offs;
+        int w = 0;
+        rc = run_tiled_group(classes[c], sizes[c], flags, workspace, workspace_bytes, reinterpret_cast<cudaStream_t>(stream),
+                             nullptr, &ex, &w);
+        if (rc != SAL_OK) return rc;
+        writers += w;
+    }
+    if (writers_out) *writers_out = writers;
+    return SAL_OK;
 }
+
+// ---- prepared launches ----------------------------------------------------------------------
+struct sal_prepared {
+    int device;
+    int nlaunch;
+    int writers;
+    size_t ws_need;
+    BuiltLaunch launch[SAL_MAX_GROUP];
+};
+
+int sal_prepare_grouped(const sal_problem *problems, int count, unsigned flags, const sal_exchange *exchange,
+                        sal_prepared **out) {
+    if (!out) return SAL_E_NULL;
+    *out = nullptr;
+    int rc = validate_grouped(problems, count, exchange != nullptr);
+    if (rc != SAL_OK) return rc;
+    if (exchange && !exchange->gather_offsets) return SAL_E_NULL;
+    DeviceInfo *dev = nullptr;
+    rc = device_info(&dev);
+    if (rc != SAL_OK) return rc;
+    sal_prepared *h = new (std::nothrow) sal_prepared();
+    if (!h) return SAL_E_LAUNCH;
+    cudaGetDevice(&h->device);
+    sal_problem classes[SAL_MAX_GROUP][SAL_MAX_GROUP];
+    int sizes[SAL_MAX_GROUP], index[SAL_MAX_GROUP][SAL_MAX_GROUP];
+    h->nlaunch = split_by_q(problems, count, classes, sizes, index);
+    for (int c = 0; c < h->nlaunch; ++c) {
+        long long offs[SAL_MAX_GROUP];
+        sal_exchange ex;
+        if (exchange) {
+            for (int i = 0; i < sizes[c]; ++i) offs[i] = exchange->gather_offsets[index[c][i]];
+            ex = *exchange;
+            ex.gather_offsets = offs;
+            if (ex.slot < 0) ex.slot = 0;
+        }
+        rc = build_tiled_group(classes[c], sizes[c], flags, true, true, exchange ? &ex : nullptr, nullptr, &h->launch[c]);
+        if (rc != SAL_OK) {
+            delete h;
+            return rc;
+        }
+        h->writers += h->launch[c].writers;
+        if (h->launch[c].ws_need > h->ws_need) h->ws_need = h->launch[c].ws_need;
+    }
+    *out = h;
+    return SAL_OK;
+}
+
+size_t sal_prepared_workspace_bytes(const sal_prepared *prepared) { return prepared ? (prepared->ws_need ? prepared->ws_need : WS_PARTIAL_OFFSET) : 0; }
+
+int sal_prepared_writers(const sal_prepared *prepared) { return prepared ? prepared->writers : 0; }
+
+int sal_launch_prepared(const sal_prepared *prepared, void *workspace, size_t workspace_bytes, int slot, void *stream) {
+    if (!prepared) return SAL_E_NULL;
+    int dev = -1;
+    if (!cuda_ok(cudaGetDevice(&dev)) || dev != prepared->device) return SAL_E_DEVICE;
+    for (int c = 0; c < prepared->nlaunch; ++c) {
+        const int rc = launch_built(prepared->launch[c], workspace, workspace_bytes, slot, reinterpret_cast<cudaStream_t>(stream));
+        if (rc != SAL_OK) return rc;
+    }
+    return SAL_OK;
+}
+
+void sal_destroy_prepared(sal_prepared *prepared) { delete prepared; }
 
 int sal_exchange_wait(void *local_flags, int slot, unsigned expected, void *workspace, void *stream) {
     if (!local_flags) return SAL_E_NULL;
@@ -1828,10 +1980,19 @@ int sal_lutgemv_shift_scale_static(const void *bw, const void *alpha, const void
     }
     void *ws = g_static_scratch_addr[dev];
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
-    // The array keeps whatever the previous call left: the status word and the arrival counters
-    // must start at zero (a call that was cut short could have left counters half way).
-    if (!cuda_ok(cudaMemsetAsync(ws, 0, WS_PARTIAL_OFFSET, s))) return SAL_E_LAUNCH;
+    // The array keeps whatever the previous call left.  The arrival counters must start at zero (a call that
+    // was cut short could have left them half way); the status word in the header is left alone, so that a
+    // device-side SAL_E_TIMEOUT / SAL_E_UNSUPPORTED stays readable through sal_static_status.
+    if (!cuda_ok(cudaMemsetAsync(static_cast<char *>(ws) + WS_HEADER_BYTES, 0, WS_COUNTER_BYTES, s))) return SAL_E_LAUNCH;
     return sal_lutgemv_shift_scale(bw, alpha, bias, x, y, M, K, N, q, num_groups, flags, ws, sizeof(g_static_scratch), s);
+}
+
+// Status word of the built-in scratch of the current device, read back (synchronously, on `stream`) and cleared.
+int sal_static_status(void *stream) {
+    int dev = 0;
+    if (!cuda_ok(cudaGetDevice(&dev)) || dev < 0 || dev >= 64) return SAL_E_DEVICE;
+    if (g_static_scratch_addr[dev] == nullptr) return SAL_OK;  // no call on this device yet: nothing recorded
+    return sal_workspace_status(g_static_scratch_addr[dev], stream);
 }
 
 }  // extern "C"

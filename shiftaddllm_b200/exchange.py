@@ -63,36 +63,28 @@ class PeerExchange:
         return [cls(world, r, bufs, flgs, r) for r in range(world)]
 
     # ---- launches -----------------------------------------------------------------------
-    def launch(self, problems, gather_offsets: Sequence[int], slot: int, *, pdl: bool = False) -> int:
-        """Grouped mode-A launch with the fused exchange.  `problems` as for
-        lutgemm.lutgemv_grouped (mSize = LOCAL width); `gather_offsets[i]` = element offset of
-        problem i's [world][mSize] block in the gather buffers.  Returns this rank's arrivals."""
-        lib = _lib.load()
-        arr = (_lib.SalProblem * len(problems))()
-        n_total = 0
-        for i, p in enumerate(problems):
-            bias = p.get("bias")
-            arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
-                                     bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
-                                     p["output"].data_ptr(), 1, int(p["kSize"]), int(p["mSize"]), int(p["nb"]),
-                                     int(p["num_groups"]), None)
-            n_total += int(p["mSize"])
-        offs = (ctypes.c_longlong * len(problems))(*[int(o) for o in gather_offsets])
+    def _descriptor(self, gather_offsets: Sequence[int], slot: int):
+        offs = (ctypes.c_longlong * len(gather_offsets))(*[int(o) for o in gather_offsets])
         ex = _lib.SalExchange()
         ex.world, ex.rank, ex.slot = self.world, self.rank, int(slot)
         for t in range(self.world):
             ex.peer_buffers[t] = self._buffer_ptrs[t]
             ex.peer_flags[t] = self._flag_ptrs[t]
         ex.gather_offsets = offs
-        writers = ctypes.c_int(0)
-        dev = problems[0]["output"].device
-        with torch.cuda.device(dev):
-            ws = lutgemm.workspace_for(dev, 1, n_total)
-            stream = torch.cuda.current_stream(dev).cuda_stream
-            _lib.check(lib.sal_lutgemv_grouped_exchange(arr, len(problems), _lib.SAL_PDL if pdl else 0, ws.data_ptr(),
-                                                        ws.numel(), ctypes.byref(ex), ctypes.byref(writers), stream),
-                       "sal_lutgemv_grouped_exchange")
-        return writers.value
+        return ex, offs
+
+    def prepare(self, problems, gather_offsets: Sequence[int], *, pdl: bool = False) -> "lutgemm.GroupedLaunch":
+        """Grouped mode-A launch with the fused exchange, prepared once (arguments marshalled, work split
+        planned, descriptors encoded).  `problems` as for lutgemm.lutgemv_grouped (mSize = LOCAL width);
+        `gather_offsets[i]` = element offset of problem i's [world][mSize] block in the gather buffers.
+        Call the result with the counter slot of the launch; `.writers` = this rank's arrivals per launch."""
+        return lutgemm.GroupedLaunch(problems, pdl=pdl, exchange=self._descriptor(gather_offsets, 0))
+
+    def launch(self, problems, gather_offsets: Sequence[int], slot: int, *, pdl: bool = False) -> int:
+        """One-off form of `prepare` + call.  Returns this rank's arrivals."""
+        prepared = self.prepare(problems, gather_offsets, pdl=pdl)
+        prepared(int(slot))
+        return prepared.writers
 
     def wait(self, slot: int, writers_per_rank: int):
         """Enqueues the wait for all ranks' arrivals on counter `slot` (and its reset)."""

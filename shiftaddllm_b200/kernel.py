@@ -3,7 +3,8 @@
 Mirrors the interface of the reference's ``lut_gemm/kernel.py`` — same function
 names, argument meaning and tensor layouts — with vectorised torch code that
 runs on whatever device its inputs live on.  Integer results are bit-exact
-with the reference functions (see tests/test_packing.py).
+with the reference functions (see tests/test_host_logic.py for the CPU code and
+tests/test_gpu_packing.py for the CUDA packers).
 """
 from __future__ import annotations
 
@@ -16,7 +17,7 @@ from .quant import LutLinear, make_lut
 
 __all__ = [
     "pack_binaryWeight", "pack_to_kernel_layout", "unpack_weight", "unpack_to_fake_binaryWeight", "convert_weight", "to_kernel_layout",
-    "find_layers", "load_shiftaddllm_weight", "load_shiftaddllm_weight_with_kernel",
+    "find_layers", "load_shiftaddllm_weight", "load_shiftaddllm_weight_with_kernel", "save_lat_checkpoint",
 ]
 
 
@@ -172,6 +173,41 @@ def _decoder_layers(model):
 
 def _ckpt_path(weights_dir, model_name, layer_name, wbits):
     return os.path.join(weights_dir, f"{model_name}_{layer_name}_{wbits}bit.pt")
+
+
+def save_lat_checkpoint(planes: torch.Tensor, alpha: torch.Tensor, weights_dir, model_name, layer_name, wbits=None,
+                        invperm: torch.Tensor | None = None) -> str:
+    """Writes one layer's "Lat." checkpoint file, the format the loaders below read: the step that ends
+    the reference's block-wise quantisation (quant_methods/shiftaddllm.py:191-211).
+
+    ``planes``: +-1 values ``[K_in, N_out/gs, gs, wbits]`` (one row per INPUT feature, columns in groups of
+    ``gs`` outputs); ``alpha``: ``[K_in/8, N_out/gs, wbits]``, one scale per block of 8 inputs x gs outputs.
+    ``invperm`` (optional, ``[K_in/8]``): with activation ordering the quantiser works on permuted blocks of
+    8 input rows; this is the inverse permutation that puts blocks — of the planes and of alpha alike — back
+    in model order before packing (shiftaddllm.py:195-201).
+    The planes are packed along out_features with :func:`pack_binaryWeight` (on the GPU for CUDA tensors) to
+    int32 ``[K_in, N_out/32, wbits]``; the file ``{weights_dir}/{model_name}_{layer_name}_{wbits}bit.pt`` holds
+    ``{"bWeight": ..., "alpha": ...}`` on the CPU.  Returns the path."""
+    if planes.dim() != 4 or alpha.dim() != 3:
+        raise ValueError("planes must be [K_in, N_out/gs, gs, wbits] and alpha [K_in/8, N_out/gs, wbits]")
+    k_in, n_group, gs, q = planes.shape
+    if wbits is None:
+        wbits = q
+    if q != wbits:
+        raise ValueError(f"Weight bit mismatch, expect {wbits} bits, but got {q} bits")
+    if k_in % 8 or tuple(alpha.shape) != (k_in // 8, n_group, q):
+        raise ValueError(f"alpha must be [{k_in // 8}, {n_group}, {q}], got {tuple(alpha.shape)}")
+    if (n_group * gs) % 32:
+        raise ValueError("out_features must be a multiple of 32")
+    if invperm is not None:
+        invperm = invperm.to(planes.device)
+        planes = planes.reshape(k_in // 8, 8, n_group, gs, q)[invperm].reshape(k_in, n_group, gs, q)
+        alpha = alpha[invperm.to(alpha.device)]
+    packed = pack_binaryWeight(planes)
+    os.makedirs(weights_dir, exist_ok=True)
+    path = _ckpt_path(weights_dir, model_name, layer_name, wbits)
+    torch.save({"bWeight": packed.cpu(), "alpha": alpha.detach().float().cpu()}, path)
+    return path
 
 
 def load_shiftaddllm_weight(model, weights_dir, model_name, wbits, is_lat=False):

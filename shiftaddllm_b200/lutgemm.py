@@ -13,6 +13,8 @@ the legacy default stream; accumulation is fp32 and deterministic; batch
 """
 from __future__ import annotations
 
+import ctypes
+import os
 import sys
 
 import torch
@@ -20,21 +22,29 @@ import torch
 from . import _lib
 
 _workspaces: dict = {}
+_superseded: list = []   # outgrown scratch buffers: kept alive, a CUDA graph captured earlier may still name them
 
 
-def workspace_for(device: torch.device, m: int, n: int) -> torch.Tensor:
+def workspace_bytes(device: torch.device, need: int) -> torch.Tensor:
     """Zero-initialised scratch for the split-K reduction, cached per
     (device, stream) and grown on demand.  Calls on one stream are ordered, so
-    sharing one buffer per stream is race-free."""
-    lib = _lib.load()
+    sharing one buffer per stream is race-free.  A buffer that is outgrown is
+    kept (not freed): launches captured into a CUDA graph keep using the address
+    they were captured with, and the old buffer stays valid for them."""
     stream = torch.cuda.current_stream(device).cuda_stream
     key = (device.index if device.index is not None else torch.cuda.current_device(), stream)
-    need = lib.sal_workspace_bytes(m, n)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < need:
+        if ws is not None:
+            _superseded.append(ws)
         ws = torch.zeros(need, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def workspace_for(device: torch.device, m: int, n: int) -> torch.Tensor:
+    """Scratch large enough for a product (or a group of products) with `m` rows and `n` columns in all."""
+    return workspace_bytes(device, _lib.load().sal_workspace_bytes(m, n))
 
 
 def _req(t: torch.Tensor, dtype, name: str) -> None:
@@ -153,63 +163,79 @@ def lutgemm_block_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb,
         raise RuntimeError(f"unsupported alpha dtype {alpha.dtype}")
 
 
-class GroupedLaunch:
-    """A grouped launch whose argument block was validated and marshalled once
-    (``prepare_grouped``); calling it enqueues the launch on the current stream
-    of the tensors' device.  The tensors named at preparation are referenced,
-    not copied: their storage must stay where it is."""
+def marshal_problems(problems, *, atomic_f32=False, swiglu_f32=False):
+    """Checks the tensors of a grouped launch and returns (ctypes array, tensors to keep alive)."""
+    if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
+        raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
+    arr = (_lib.SalProblem * len(problems))()
+    keep = []
+    out_dtype = torch.float32 if atomic_f32 else torch.float16
+    in_dtype = torch.float32 if swiglu_f32 else torch.float16
+    for i, p in enumerate(problems):
+        _req(p["output"], out_dtype, "output")
+        _req(p["bWeight"], torch.int32, "bWeight")
+        _req(p["alpha"], torch.float16, "alpha")
+        _req(p["d_input"], in_dtype, "d_input")
+        n, k = int(p["mSize"]), int(p["kSize"])
+        m = _rows(p["output"], p["d_input"], n, k)
+        bias = p.get("bias")
+        mul = p.get("d_input_mul")      # optional: the activation is silu(d_input) * d_input_mul
+        if mul is not None:
+            _req(mul, in_dtype, "d_input_mul")
+            if mul.numel() != p["d_input"].numel():
+                raise RuntimeError("d_input_mul must have the shape of d_input")
+        arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
+                                 bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
+                                 p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]),
+                                 mul.data_ptr() if mul is not None else None)
+        keep.append((p["output"], p["bWeight"], p["alpha"], bias, p["d_input"], mul))
+    return arr, keep
 
-    def __init__(self, problems, *, pdl=False, accumulate=False, atomic_f32=False, swiglu_f32=False):
+
+class GroupedLaunch:
+    """A grouped launch prepared once (``sal_prepare_grouped``: arguments validated, work split
+    planned, tensor-map descriptors encoded); calling it enqueues the launch on the current stream
+    of the tensors' device.  The tensors named at preparation are referenced, not copied: their
+    storage must stay where it is.  Problems may differ in ``nb`` (mixed precision): the launch is
+    then one kernel per distinct plane count."""
+
+    def __init__(self, problems, *, pdl=False, accumulate=False, atomic_f32=False, swiglu_f32=False, exchange=None):
         self._lib = _lib.load()
-        if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
-            raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
-        self._arr = (_lib.SalProblem * len(problems))()
-        self._count = len(problems)
+        self._arr, self._keep = marshal_problems(problems, atomic_f32=atomic_f32, swiglu_f32=swiglu_f32)
         self._device = problems[0]["output"].device
-        self._keep = []          # keeps the tensors (and with them the addresses in _arr) alive
-        self._n_total = 0
-        self._m_max = 1
-        out_dtype = torch.float32 if atomic_f32 else torch.float16
-        in_dtype = torch.float32 if swiglu_f32 else torch.float16
-        for i, p in enumerate(problems):
-            _req(p["output"], out_dtype, "output")
-            _req(p["bWeight"], torch.int32, "bWeight")
-            _req(p["alpha"], torch.float16, "alpha")
-            _req(p["d_input"], in_dtype, "d_input")
-            n, k = int(p["mSize"]), int(p["kSize"])
-            m = _rows(p["output"], p["d_input"], n, k)
-            self._m_max = max(self._m_max, m)
-            bias = p.get("bias")
-            mul = p.get("d_input_mul")      # optional: the activation is silu(d_input) * d_input_mul
-            if mul is not None:
-                _req(mul, in_dtype, "d_input_mul")
-                if mul.numel() != p["d_input"].numel():
-                    raise RuntimeError("d_input_mul must have the shape of d_input")
-            self._arr[i] = _lib.SalProblem(p["bWeight"].data_ptr(), p["alpha"].data_ptr(),
-                                           bias.data_ptr() if bias is not None else None, p["d_input"].data_ptr(),
-                                           p["output"].data_ptr(), m, k, n, int(p["nb"]), int(p["num_groups"]),
-                                           mul.data_ptr() if mul is not None else None)
-            self._keep.append((p["output"], p["bWeight"], p["alpha"], bias, p["d_input"], mul))
-            self._n_total += n
-        self._flags = ((_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
-                       | (_lib.SAL_OUT_F32_ATOMIC if atomic_f32 else 0) | (_lib.SAL_SWIGLU_F32 if swiglu_f32 else 0))
-        self._fn = self._lib.sal_lutgemv_grouped
-        self._need = self._lib.sal_workspace_bytes(self._m_max, self._n_total)
         if self._device.index is None:
             self._device = torch.device("cuda", torch.cuda.current_device())
+        self._flags = ((_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
+                       | (_lib.SAL_OUT_F32_ATOMIC if atomic_f32 else 0) | (_lib.SAL_SWIGLU_F32 if swiglu_f32 else 0))
+        self._exchange = exchange          # a ctypes SalExchange (and what it points to), or None
+        handle = _lib._vp()
+        with torch.cuda.device(self._device):
+            rc = self._lib.sal_prepare_grouped(self._arr, len(problems), self._flags,
+                                               ctypes.byref(exchange[0]) if exchange is not None else None, ctypes.byref(handle))
+        if rc != 0:
+            _lib.check(rc, "sal_prepare_grouped")
+        self._handle = handle
+        self._need = self._lib.sal_prepared_workspace_bytes(handle)
+        self.writers = self._lib.sal_prepared_writers(handle)
+        self._launch = self._lib.sal_launch_prepared
 
-    def __call__(self):
+    def __call__(self, slot: int = -1):
         dev = self._device
         if torch.cuda.current_device() != dev.index:
             with torch.cuda.device(dev):
-                return self()
+                return self(slot)
         stream = torch.cuda.current_stream(dev).cuda_stream
         ws = _workspaces.get((dev.index, stream))
         if ws is None or ws.numel() < self._need:
-            ws = workspace_for(dev, self._m_max, self._n_total)
-        rc = self._fn(self._arr, self._count, self._flags, ws.data_ptr(), ws.numel(), stream)
+            ws = workspace_bytes(dev, self._need)
+        rc = self._launch(self._handle, ws.data_ptr(), ws.numel(), slot, stream)
         if rc != 0:
-            _lib.check(rc, "sal_lutgemv_grouped")
+            _lib.check(rc, "sal_launch_prepared")
+
+    def __del__(self):
+        handle, self._handle = getattr(self, "_handle", None), None
+        if handle:
+            self._lib.sal_destroy_prepared(handle)
 
 
 def prepare_grouped(problems, **kwargs) -> GroupedLaunch:
@@ -230,7 +256,27 @@ def lutgemv_grouped(problems, *, pdl=False, accumulate=False, atomic_f32=False, 
     GroupedLaunch(problems, pdl=pdl, accumulate=accumulate, atomic_f32=atomic_f32, swiglu_f32=swiglu_f32)()
 
 
-def install(name: str = "lutgemm") -> None:
-    """Registers this module as ``lutgemm`` so that unmodified reference code
-    (``import lutgemm`` in lut_gemm/quant.py:5) binds to the sm_100a library."""
-    sys.modules[name] = sys.modules[__name__]
+def compiled_module():
+    """The compiled `lutgemm` extension module (pybind11 + torch tensors over the C ABI; built by
+    ``python -m shiftaddllm_b200.build`` into ``shiftaddllm_b200/ext/``), imported from there."""
+    import importlib.util
+
+    from . import build
+
+    path = build.extension_path()
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: build it with `python -m shiftaddllm_b200.build`")
+    spec = importlib.util.spec_from_file_location("lutgemm", path)
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def install(name: str = "lutgemm", compiled: bool = True):
+    """Makes ``import lutgemm`` (lut_gemm/quant.py:5) bind to this build, so that unmodified reference
+    code runs on the sm_100a library.  ``compiled=True`` registers the compiled extension module — what
+    lut_gemm/setup_lut.py installs for the reference; ``compiled=False`` registers this Python module
+    (same five functions through ctypes).  Returns the registered module."""
+    module = compiled_module() if compiled else sys.modules[__name__]
+    sys.modules[name] = module
+    return module

@@ -23,6 +23,8 @@ def golden():
 def lib():
     from shiftaddllm_b200 import _lib, build
 
-    if not os.path.exists(build.LIB):   # a prebuilt library (the one shipped to the GPU box) is used as it is
+    # a library older than its sources would be tested silently: rebuild it (nvcc is in the image; the
+    # library shipped to a GPU box is newer than the sources it was built from and is used as it is)
+    if not build.up_to_date():
         build.build()
     return _lib.load()

@@ -16,6 +16,7 @@ def declared_functions():
     for header in ("sal_lutgemm.h", "sal_decode_ops.h", "sal_pack.h"):
         text = open(os.path.join(REPO, "include", header)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = re.sub(r"#ifdef SAL_MEASURE.*?#endif", "", text, flags=re.S)   # declared for measurement builds only
         names |= set(re.findall(r"\b(sal_[a-z0-9_]+)\s*\(", text))
     return sorted(names)
 
@@ -69,7 +70,14 @@ def test_argument_validation_happens_before_any_gpu_work(lib):
     probs = (_lib.SalProblem * 1)()
     assert lib.sal_lutgemv_grouped(probs, 0, 0, None, 0, None) == _lib.SAL_E_SHAPE
     assert lib.sal_lutgemv_grouped(probs, 9, 0, None, 0, None) == _lib.SAL_E_SHAPE
-    assert lib.sal_debug_set(b"no-such-key", 1) == _lib.SAL_E_UNSUPPORTED
+    assert lib.sal_prepare_grouped(None, 1, 0, None, ctypes.byref(ctypes.c_void_p())) == _lib.SAL_E_NULL
+    assert lib.sal_launch_prepared(None, None, 0, -1, None) == _lib.SAL_E_NULL
+    assert lib.sal_prepared_workspace_bytes(None) == 0
+
+
+def test_measurement_hook_is_not_in_the_product_library(lib):
+    """The switches that turn parts of the kernel off for timing exist only in -DSAL_MEASURE builds."""
+    assert not hasattr(lib, "sal_debug_set")
 
 
 def test_no_cpu_fallback(lib):

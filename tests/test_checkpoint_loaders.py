@@ -30,8 +30,11 @@ def write_checkpoints(model, directory, name="opt-tiny"):
             k_in, n_out = lin.in_features, lin.out_features
             planes = torch.randint(0, 2, (k_in, n_out // GS, GS, WBITS), generator=gen, dtype=torch.int8) * 2 - 1
             alpha = torch.exp2(-torch.randint(3, 8, (k_in // 8, n_out // GS, WBITS), generator=gen).float())
-            packed = K.pack_binaryWeight(planes)                              # [K_in, N_out/32, q]
-            torch.save({"bWeight": packed, "alpha": alpha}, f"{directory}/{name}_{i}.{lname}_{WBITS}bit.pt")
+            # the product-side writer (quant_methods/shiftaddllm.py:191-211): packs along out_features, saves
+            path = K.save_lat_checkpoint(planes, alpha, str(directory), name, f"{i}.{lname}", WBITS)
+            assert path == f"{directory}/{name}_{i}.{lname}_{WBITS}bit.pt"
+            packed = torch.load(path)["bWeight"]                                 # [K_in, N_out/32, q]
+            assert packed.dtype == torch.int32 and tuple(packed.shape) == (k_in, n_out // 32, WBITS)
             w_t = o.unpack_weight(packed.numpy(), np.repeat(alpha.numpy(), 8, axis=0))   # [K_in, N_out] via the oracle
             dense[(i, lname)] = torch.from_numpy(np.ascontiguousarray(w_t.T))
     return dense
@@ -70,6 +73,36 @@ def test_kernel_load_builds_lutlinear_with_converted_layout(tmp_path):
     shutil.copy(f"{tmp_path}/opt-tiny_0.{first}_{WBITS}bit.pt", f"{tmp_path}/opt-tiny_0.{first}_2bit.pt")
     with pytest.raises(ValueError):
         K.load_shiftaddllm_weight_with_kernel(tiny_opt(), str(tmp_path), "opt-tiny", 2, is_lat=True)
+
+
+def test_checkpoint_writer_undoes_the_activation_order(tmp_path):
+    """With act-order the quantiser sees blocks of 8 input rows in permuted order; the writer puts planes and
+    alpha back in model order (quant_methods/shiftaddllm.py:195-201).  Checked against the oracle's packer."""
+    gen = torch.Generator().manual_seed(11)
+    k_in, n_out = 64, 96
+    planes = torch.randint(0, 2, (k_in, n_out // GS, GS, WBITS), generator=gen, dtype=torch.int8) * 2 - 1
+    alpha = torch.rand(k_in // 8, n_out // GS, WBITS, generator=gen)
+    perm = torch.randperm(k_in // 8, generator=gen)
+    invperm = torch.argsort(perm)
+    permuted_planes = planes.reshape(k_in // 8, 8, -1)[perm].reshape(planes.shape)     # what the quantiser produced
+    path = K.save_lat_checkpoint(permuted_planes, alpha[perm], str(tmp_path), "m", "0.fc1", invperm=invperm)
+    ckpt = torch.load(path)
+    assert np.array_equal(ckpt["bWeight"].numpy(), o.pack_binary_weight(planes.numpy()))
+    assert torch.equal(ckpt["alpha"], alpha)
+    with pytest.raises(ValueError):
+        K.save_lat_checkpoint(planes, alpha, str(tmp_path), "m", "0.fc1", wbits=2)
+    with pytest.raises(ValueError):
+        K.save_lat_checkpoint(planes, alpha[:-1], str(tmp_path), "m", "0.fc1")
+
+
+@pytest.mark.gpu
+def test_checkpoint_writer_packs_on_the_gpu(tmp_path):
+    gen = torch.Generator().manual_seed(12)
+    planes = torch.randint(0, 2, (256, 16, GS, WBITS), generator=gen, dtype=torch.int8) * 2 - 1
+    alpha = torch.rand(32, 16, WBITS, generator=gen)
+    a = torch.load(K.save_lat_checkpoint(planes, alpha, str(tmp_path), "cpu", "0.q"))
+    b = torch.load(K.save_lat_checkpoint(planes.cuda(), alpha.cuda(), str(tmp_path), "gpu", "0.q"))
+    assert torch.equal(a["bWeight"], b["bWeight"]) and torch.equal(a["alpha"], b["alpha"]) and not b["bWeight"].is_cuda
 
 
 @pytest.mark.gpu

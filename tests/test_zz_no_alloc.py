@@ -44,6 +44,26 @@ def test_static_scratch_matches_workspace_entry_twice():
             assert np.isfinite(a).all()
             assert o.max_rel_err(a, b) <= TOL
             assert np.array_equal(a, b)        # same kernel, same fixed reduction order
+    stream = torch.cuda.current_stream().cuda_stream
+    assert lib.sal_static_status(stream) == 0          # no bounded wait expired, no unsupported variant ran
+    # the contract itself: after the first call on the device, a call takes no device memory at all
+    layer, d = layers[0], layers[0].to("cuda")
+    y_st = torch.empty(1, layer.N, dtype=torch.float16, device="cuda")
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    torch_before = torch.cuda.memory_allocated()
+    for _ in range(3):
+        assert _call_static(lib, layer, d, y_st) == 0
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] == free_before and torch.cuda.memory_allocated() == torch_before
+    assert lib.sal_static_status(stream) == 0
+    layer = layers[1]
+    a = None
+    d = layer.to("cuda")
+    y_st = torch.empty(1, layer.N, dtype=torch.float16, device="cuda")
+    assert _call_static(lib, layer, d, y_st) == 0
+    torch.cuda.synchronize()
+    a = y_st.float().cpu().numpy()
     # and against the oracle once, so that both being wrong together cannot pass
     layer = layers[1]
     w = o.dequant_mode_a(layer.bWeight.numpy(), layer.alpha.numpy())
