@@ -8,9 +8,11 @@
 // once and never dequantised.
 //
 // Tiled kernel (M = 1, mode A), per CTA:
-//   * one producer thread issues tiled TMA copies (cp.async.bulk.tensor.2d through a
-//     tensor map of the packed planes, completion on mbarrier transaction counts) of
-//     [8 words x q planes][256 columns] boxes into a shared-memory ring.  The copies do not depend on the activations, so
+//   * one producer thread issues tiled TMA copies (cp.async.bulk.tensor.3d through a
+//     tensor map of the packed planes seen as [K/32][q][N], completion on mbarrier
+//     transaction counts) of [8 words][planes][256 columns] boxes into a shared-memory
+//     ring: all planes of a (K block, column tile) unit in one slot up to q = 3 (16 or 24 KB,
+//     three or two slots), two planes per slot for q = 4.  The copies do not depend on the activations, so
 //     under programmatic dependent launch they are issued before
 //     griddepcontrol.wait and overlap the previous kernel's tail.  A CTA uses
 //     at most half of an SM's shared memory, so the CTAs of two consecutive
@@ -99,8 +101,8 @@ struct ExchangeParams {
 };
 
 struct TileParams {
-    // One tiled-TMA descriptor per problem: the packed planes seen as a 2-D uint32 tensor
-    // [rows = (K/32)*q][columns = N], box = [8*q rows][256 columns] = one ring stage.
+    // One tiled-TMA descriptor per problem: the packed planes seen as a 3-D uint32 tensor
+    // [K/32 words][q planes][N columns], box = [8 words][PPS planes][256 columns] = one ring slot.
     alignas(64) CUtensorMap tmap[SAL_MAX_GROUP];
     TileProblem p[SAL_MAX_GROUP];
     int count;
@@ -192,12 +194,12 @@ __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-// Tiled TMA load of one 2-D box (no multicast).  x is the innermost (column) coordinate in
-// elements and must keep x * 4 bytes a multiple of 16; y is the row coordinate.
-__device__ __forceinline__ void tma_tile_2d_g2s(uint32_t dst, const CUtensorMap *tmap, int x, int y, uint32_t bar) {
+// Tiled TMA load of one 3-D box (no multicast).  x is the innermost (column) coordinate in
+// elements and must keep x * 4 bytes a multiple of 16; y is the plane, z the first 32-bit word of K.
+__device__ __forceinline__ void tma_tile_3d_g2s(uint32_t dst, const CUtensorMap *tmap, int x, int y, int z, uint32_t bar) {
     asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
-        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(bar)
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(bar)
         : "memory");
 }
 __device__ __forceinline__ void fence_barrier_init() {
@@ -215,9 +217,11 @@ __device__ __forceinline__ void consumer_barrier(int nthreads) {
 template <int Q, int NCW>
 struct TileCfg {
     static constexpr int CW = NCW * 32;             // columns per stage
-    static constexpr int W_ROWS = KB_WORDS * Q;     // weight rows per stage
+    static constexpr int PPS = (Q == 4 ? 2 : Q);    // planes per ring slot: all of them up to q = 3, two slots per unit for q = 4
+    static constexpr int SLOTS = Q / PPS;           // ring slots per (K block, column tile) unit
+    static constexpr int W_ROWS = KB_WORDS * PPS;   // weight rows per slot: [8 words][PPS planes]
     static constexpr int STAGE_BYTES = W_ROWS * CW * 4;
-    static constexpr int THREADS = (NCW + 1) * 32;
+    static constexpr int THREADS = (NCW + 1) * 32;   // consumer warps + the copy warp
 };
 
 // Builds the 32 tables of one K block.  Lane = chunk; a warp handles groups of
@@ -422,28 +426,48 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         for (int kb = kb_begin; kb < kb_end; ++kb) {
             const int s_lo = kb == kb_begin ? t_first : 0, s_hi = kb == kb_last ? t_last + 1 : nsub;
             for (int sub = s_lo; sub < s_hi; ++sub) {
-                if (!first_round) mbar_wait(empty0 + 8 * st, phase, P.status);
                 const int n0 = (sub_begin + sub) * CW;
-                const uint32_t full = full0 + 8 * st;
-                if (lane == 0) {
-                    // columns past N are zero-filled by the TMA unit and still counted
-                    mbar_expect_tx(full, (uint32_t)C::STAGE_BYTES);
+#pragma unroll 1
+                for (int b = 0; b < Q; b += C::PPS) {   // one slot per PPS planes
+                    if (!first_round) mbar_wait(empty0 + 8 * st, phase, P.status);
+                    const uint32_t full = full0 + 8 * st;
+                    if (lane == 0) {
+                        // columns past N are zero-filled by the TMA unit and still counted
+                        mbar_expect_tx(full, (uint32_t)C::STAGE_BYTES);
 #pragma unroll
-                    for (int bx = 0; bx < CW / BOX_COLS; ++bx)
-                        tma_tile_2d_g2s(stage_s + (uint32_t)st * C::STAGE_BYTES + (uint32_t)bx * (C::W_ROWS * BOX_COLS * 4),
-                                        &P.tmap[pi], n0 + bx * BOX_COLS, kb * C::W_ROWS, full);
-                }
-                __syncwarp();
-                if (++st == stages) {
-                    st = 0;
-                    if (first_round) first_round = false;
-                    else phase ^= 1u;
+                        for (int bx = 0; bx < CW / BOX_COLS; ++bx)
+                            tma_tile_3d_g2s(stage_s + (uint32_t)st * C::STAGE_BYTES + (uint32_t)bx * (C::W_ROWS * BOX_COLS * 4),
+                                            &P.tmap[pi], n0 + bx * BOX_COLS, b, kb * KB_WORDS, full);
+                    }
+                    __syncwarp();
+                    if (++st == stages) {
+                        st = 0;
+                        if (first_round) first_round = false;
+                        else phase ^= 1u;
+                    }
                 }
             }
         }
         return;
     }
 
+    const __half *xrow0 = pr.x + (size_t)row0 * pr.K;
+    const __half *xrow1 = pr.x + (size_t)(row0 + (rows_here > 1 ? 1 : 0)) * pr.K;  // odd M: the last pair repeats its row
+    // Tables of K block `kb` into table half `half`, by `nwarps` warps of which this is number `w`.
+    auto build_block = [&](int kb, int half, int w, auto nwarps_tag) {
+        constexpr int NW = decltype(nwarps_tag)::value;
+        const size_t ko = (size_t)kb * KB_FEATS;
+        if (SWIGLU == 2) {   // fp32 operands: same element offsets, twice the bytes (pointers are carried as __half*)
+            const __half *g32 = pr.x + 2 * ((xrow0 - pr.x) + ko);
+            const __half *u32 = pr.x_mul + 2 * ((xrow0 - pr.x) + ko);
+            build_tables_impl<NW, ROWS, SWIGLU>(g32, g32, u32, u32, lut_s + half * 128, w, lane);
+        } else {
+            // x_mul row = x_mul + (the same element offset the x row has)
+            const __half *m0 = SWIGLU ? pr.x_mul + (xrow0 - pr.x) + ko : nullptr;
+            const __half *m1 = SWIGLU ? pr.x_mul + (xrow1 - pr.x) + ko : nullptr;
+            build_tables_impl<NW, ROWS, SWIGLU>(xrow0 + ko, xrow1 + ko, m0, m1, lut_s + half * 128, w, lane);
+        }
+    };
     // -------------------------------- consumer warps --------------------------------
     const int col = warp * 32 + lane;
     const int hw = lane >> 4;
@@ -465,7 +489,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int wi = 4 * (hp ^ hw) + ((j + rot) & 3);
-            wrow[hp][j] = stage_s + (unsigned)(((col / BOX_COLS) * (C::W_ROWS * BOX_COLS) + wi * Q * BOX_COLS + (col % BOX_COLS)) * 4);
+            wrow[hp][j] = stage_s + (unsigned)(((col / BOX_COLS) * (C::W_ROWS * BOX_COLS) + wi * C::PPS * BOX_COLS + (col % BOX_COLS)) * 4);
             unsigned pk = 0;
 #pragma unroll
             for (int t = 0; t < 4; ++t) pk |= (unsigned)(16 * wi + 4 * ((t + s4) & 3)) << (8 * t);
@@ -616,28 +640,13 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
 
     pdl_wait();  // activations, bias, y and the scratch buffer may be written by the previous kernel
 
-    const __half *xrow0 = pr.x + (size_t)row0 * pr.K;
-    const __half *xrow1 = pr.x + (size_t)(row0 + (rows_here > 1 ? 1 : 0)) * pr.K;  // odd M: the last pair repeats its row
     int st = 0;
     uint32_t phase = 0;
     // One K block: build its tables into half `PAR` of the table rows, then walk the column tiles.
     auto process_block = [&](int kb, auto par_tag) {
         constexpr int PAR = BLK ? 0 : decltype(par_tag)::value;
         if constexpr (BLK) consumer_barrier(NCW * 32);  // one set of tables: the previous K block must be finished by all
-        if (!SAL_ABLATED(P, 2))
-        {
-            const size_t ko = (size_t)kb * KB_FEATS;
-            if (SWIGLU == 2) {   // fp32 operands: same element offsets, twice the bytes (pointers are carried as __half*)
-                const __half *g32 = pr.x + 2 * ((xrow0 - pr.x) + ko);
-                const __half *u32 = pr.x_mul + 2 * ((xrow0 - pr.x) + ko);
-                build_tables_impl<NCW, ROWS, SWIGLU>(g32, g32, u32, u32, lut_s + PAR * 128, warp, lane);
-            } else {
-                // x_mul row = x_mul + (the same element offset the x row has)
-                const __half *m0 = SWIGLU ? pr.x_mul + (xrow0 - pr.x) + ko : nullptr;
-                const __half *m1 = SWIGLU ? pr.x_mul + (xrow1 - pr.x) + ko : nullptr;
-                build_tables_impl<NCW, ROWS, SWIGLU>(xrow0 + ko, xrow1 + ko, m0, m1, lut_s + PAR * 128, warp, lane);
-            }
-        }
+        if (!SAL_ABLATED(P, 2)) build_block(kb, PAR, warp, std::integral_constant<int, NCW>{});
         consumer_barrier(NCW * 32);
         // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
         // unrolling it over the column tiles overflows the instruction cache.  acc[] is then
@@ -668,62 +677,127 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                     load_alpha(kb_n, more_sub ? sub + 1 : 0, a_next);
                 }
             }
-            mbar_wait(full0 + 8 * st, phase, P.status);
-            const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
             float a_sub[ROWS];
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) a_sub[r] = 0.f;
-            if (!SAL_ABLATED(P, 4))
+            constexpr int PPS = C::PPS;
+            if constexpr (!BLK) {
 #pragma unroll
-            for (int hp = 0; hp < 2; ++hp) {
-                float part[ROWS][Q], part2[ROWS][Q];
+                for (int b0 = 0; b0 < Q; b0 += PPS) {   // one ring slot: PPS planes of this unit
+                    mbar_wait(full0 + 8 * st, phase, P.status);
+                    const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
+                    if (!SAL_ABLATED(P, 4)) {
 #pragma unroll
-                for (int r = 0; r < ROWS; ++r)
+                        for (int hp = 0; hp < 2; ++hp) {
+                            float part[ROWS][PPS], part2[ROWS][PPS];
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) part[r][b] = part2[r][b] = 0.f;
-                // block mode: all weight words of this half are requested before the first lookup, so that the
-                // (longer) chains table load -> multiplier load -> fma of one word overlap the next word's load
-                uint32_t wpre[BLK ? 4 : 1][BLK ? Q : 1];
-                if constexpr (BLK) {
+                            for (int r = 0; r < ROWS; ++r)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint32_t wr = wrow[hp][j] + soff;
+                                for (int p = 0; p < PPS; ++p) part[r][p] = part2[r][p] = 0.f;
 #pragma unroll
-                        for (int b = 0; b < Q; ++b) {
-                            if (b == 0) wpre[j][b] = lds_u32_imm<0>(wr);
-                            else if (b == 1) wpre[j][b] = lds_u32_imm<1 * BOX_COLS * 4>(wr);
-                            else if (b == 2) wpre[j][b] = lds_u32_imm<2 * BOX_COLS * 4>(wr);
-                            else wpre[j][b] = lds_u32_imm<3 * BOX_COLS * 4>(wr);
+                            for (int j = 0; j < 4; ++j) {
+                                const uint32_t wr = wrow[hp][j] + soff;
+#pragma unroll
+                                for (int p = 0; p < PPS; ++p) {
+                                    uint32_t w;
+                                    if (p == 0) w = lds_u32_imm<0>(wr);
+                                    else if (p == 1) w = lds_u32_imm<1 * BOX_COLS * 4>(wr);
+                                    else w = lds_u32_imm<2 * BOX_COLS * 4>(wr);
+                                    uint32_t e[4];
+#pragma unroll
+                                    for (int t = 0; t < 4; ++t) {
+                                        const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
+                                        e[t] = ABS ? lds_u32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off) : lds_u32_imm<0>(off + lut_s + PAR * 128);
+                                    }
+                                    if (ROWS == 1 && SAL_ABLATED(P, 64)) {   // timing only: integer adds (two entries per instruction)
+                                        part[0][p] = __uint_as_float(__float_as_uint(part[0][p]) + e[0] + e[2]);
+                                        part2[0][p] = __uint_as_float(__float_as_uint(part2[0][p]) + e[1] + e[3]);
+                                    } else if (ROWS == 1) {
+                                        part[0][p] += __uint_as_float(e[0]);
+                                        part2[0][p] += __uint_as_float(e[1]);
+                                        part[0][p] += __uint_as_float(e[2]);
+                                        part2[0][p] += __uint_as_float(e[3]);
+                                    } else {
+                                        // four half2 entries are added in fp16 (they are bounded by 8 max|x| each), then
+                                        // the word's sum is widened: fp32 carries everything beyond one weight word
+                                        const __half2 s01 = __hadd2(*reinterpret_cast<const __half2 *>(&e[0]), *reinterpret_cast<const __half2 *>(&e[1]));
+                                        const __half2 s23 = __hadd2(*reinterpret_cast<const __half2 *>(&e[2]), *reinterpret_cast<const __half2 *>(&e[3]));
+                                        const float2 f = __half22float2(__hadd2(s01, s23));
+                                        if (j & 1) {
+                                            part2[0][p] += f.x;
+                                            part2[ROWS - 1][p] += f.y;
+                                        } else {
+                                            part[0][p] += f.x;
+                                            part[ROWS - 1][p] += f.y;
+                                        }
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int p = 0; p < PPS; ++p) {
+                                const float a = __half2float((hp ^ hw) ? a_cur[1][b0 + p] : a_cur[0][b0 + p]);  // slot hp holds group hp ^ hw
+#pragma unroll
+                                for (int r = 0; r < ROWS; ++r) a_sub[r] += a * (part[r][p] + part2[r][p]);
+                            }
                         }
                     }
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(empty0 + 8 * st);
+                    if (++st == stages) {
+                        st = 0;
+                        phase ^= 1u;
+                    }
                 }
+            } else {
+                // block mode walks the planes innermost (the multiplier addresses of a word are shared by its
+                // planes): wait for all slots of the unit, hand them back at the end
+                constexpr int SLOTS = C::SLOTS;
+                uint32_t soffs[SLOTS];
+                int st_b = st;
+                uint32_t ph_b = phase;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint32_t wr = wrow[hp][j] + soff;
-                    uint32_t ma[4] = {0u, 0u, 0u, 0u};
-                    if constexpr (BLK) {
+                for (int i = 0; i < SLOTS; ++i) {
+                    mbar_wait(full0 + 8 * st_b, ph_b, P.status);
+                    soffs[i] = (uint32_t)st_b * C::STAGE_BYTES;
+                    if (++st_b == stages) {
+                        st_b = 0;
+                        ph_b ^= 1u;
+                    }
+                }
+                if (!SAL_ABLATED(P, 4))
+#pragma unroll
+                for (int hp = 0; hp < 2; ++hp) {
+                    float part = 0.f, part2 = 0.f;
+                    // all weight words of this half are requested before the first lookup, so that the (longer)
+                    // chains table load -> multiplier load -> fma of one word overlap the next word's load
+                    uint32_t wpre[4][Q];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j)
+#pragma unroll
+                        for (int b = 0; b < Q; ++b) {
+                            const uint32_t wr = wrow[hp][j] + soffs[b / PPS];
+                            if (b % PPS == 0) wpre[j][b] = lds_u32_imm<0>(wr);
+                            else if (b % PPS == 1) wpre[j][b] = lds_u32_imm<1 * BOX_COLS * 4>(wr);
+                            else wpre[j][b] = lds_u32_imm<2 * BOX_COLS * 4>(wr);
+                        }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
                         // multiplier address: byte 0 <- 4 * (chunk ^ group), bytes 1.. <- row of (buffer, group)
                         const uint32_t rowsel = mrow + mbuf;
+                        uint32_t ma[4];
                         ma[0] = prmt(mpack[hp][j], rowsel, 0x7650u) + (ABS ? 0u : lut_s);
                         ma[1] = prmt(mpack[hp][j], rowsel, 0x7651u) + (ABS ? 0u : lut_s);
                         ma[2] = prmt(mpack[hp][j], rowsel, 0x7652u) + (ABS ? 0u : lut_s);
                         ma[3] = prmt(mpack[hp][j], rowsel, 0x7653u) + (ABS ? 0u : lut_s);
-                    }
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) {
-                        uint32_t w;
-                        if constexpr (BLK) w = wpre[j][b];
-                        else if (b == 0) w = lds_u32_imm<0>(wr);
-                        else if (b == 1) w = lds_u32_imm<1 * BOX_COLS * 4>(wr);
-                        else if (b == 2) w = lds_u32_imm<2 * BOX_COLS * 4>(wr);
-                        else w = lds_u32_imm<3 * BOX_COLS * 4>(wr);
-                        uint32_t e[4];
+                        for (int b = 0; b < Q; ++b) {
+                            const uint32_t w = wpre[j][b];
+                            uint32_t e[4];
 #pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
-                            e[t] = ABS ? lds_u32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off) : lds_u32_imm<0>(off + lut_s + PAR * 128);
-                        }
-                        if constexpr (BLK) {
+                            for (int t = 0; t < 4; ++t) {
+                                const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
+                                e[t] = ABS ? lds_u32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off) : lds_u32_imm<0>(off + lut_s + PAR * 128);
+                            }
                             constexpr int MB = (ABS ? (int)SMEM_DYNAMIC_BASE : 0) + 128;
                             float m[4];
 #pragma unroll
@@ -733,50 +807,28 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                                 else if (b == 2) m[t] = lds_f32_imm<MB + 2 * 16 * LUT_ROW_BYTES>(ma[t]);
                                 else m[t] = lds_f32_imm<MB + 3 * 16 * LUT_ROW_BYTES>(ma[t]);
                             }
-                            part[0][0] = fmaf(m[0], __uint_as_float(e[0]), part[0][0]);
-                            part2[0][0] = fmaf(m[1], __uint_as_float(e[1]), part2[0][0]);
-                            part[0][0] = fmaf(m[2], __uint_as_float(e[2]), part[0][0]);
-                            part2[0][0] = fmaf(m[3], __uint_as_float(e[3]), part2[0][0]);
-                        } else if (ROWS == 1) {
-                            part[0][b] += __uint_as_float(e[0]);
-                            part2[0][b] += __uint_as_float(e[1]);
-                            part[0][b] += __uint_as_float(e[2]);
-                            part2[0][b] += __uint_as_float(e[3]);
-                        } else {
-                            // four half2 entries are added in fp16 (they are bounded by 8 max|x| each), then
-                            // the word's sum is widened: fp32 carries everything beyond one weight word
-                            const __half2 s01 = __hadd2(*reinterpret_cast<const __half2 *>(&e[0]), *reinterpret_cast<const __half2 *>(&e[1]));
-                            const __half2 s23 = __hadd2(*reinterpret_cast<const __half2 *>(&e[2]), *reinterpret_cast<const __half2 *>(&e[3]));
-                            const float2 f = __half22float2(__hadd2(s01, s23));
-                            if (j & 1) {
-                                part2[0][b] += f.x;
-                                part2[ROWS - 1][b] += f.y;
-                            } else {
-                                part[0][b] += f.x;
-                                part[ROWS - 1][b] += f.y;
-                            }
+                            part = fmaf(m[0], __uint_as_float(e[0]), part);
+                            part2 = fmaf(m[1], __uint_as_float(e[1]), part2);
+                            part = fmaf(m[2], __uint_as_float(e[2]), part);
+                            part2 = fmaf(m[3], __uint_as_float(e[3]), part2);
                         }
                     }
+                    a_sub[0] += part + part2;  // the multipliers are already in
                 }
-                if constexpr (BLK) {
-                    a_sub[0] += part[0][0] + part2[0][0];  // the multipliers are already in
-                } else {
+                __syncwarp();
+                if (lane == 0) {
+                    int st_r = st;
 #pragma unroll
-                    for (int b = 0; b < Q; ++b) {
-                        const float a = __half2float((hp ^ hw) ? a_cur[1][b] : a_cur[0][b]);  // slot hp holds group hp ^ hw
-#pragma unroll
-                        for (int r = 0; r < ROWS; ++r) a_sub[r] += a * (part[r][b] + part2[r][b]);
+                    for (int i = 0; i < SLOTS; ++i) {
+                        mbar_arrive(empty0 + 8 * st_r);
+                        if (++st_r == stages) st_r = 0;
                     }
                 }
+                st = st_b;
+                phase = ph_b;
             }
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) acc[r][sub] += a_sub[r];
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * st);
-            if (++st == stages) {
-                st = 0;
-                phase ^= 1u;
-            }
+            for (int r = 0; r < ROWS; ++r) acc[r][SAL_ABLATED(P, 32) ? 0 : sub] += a_sub[r];   // (timing only: no dynamic index)
             if constexpr (BLK) mbuf ^= (uint32_t)(Q * 16 * LUT_ROW_BYTES);
         }
     };
@@ -1237,16 +1289,17 @@ void plan_group(const sal_problem *problems, int count, int slots, bool allow_sp
     for (int i = 0; i < count; ++i) slot.plans[i] = plans[i];
 }
 
-int stage_bytes_for(int q, int ncw) { return KB_WORDS * q * ncw * 32 * 4; }
+int planes_per_slot(int q) { return q == 4 ? 2 : q; }
+int stage_bytes_for(int q, int ncw) { return KB_WORDS * planes_per_slot(q) * ncw * 32 * 4; }
 
 int g_stage_override = 0;  // measurement hooks (sal_debug_set)
 int g_budget_pct = 0;  // 0 = as many CTAs as can be resident (CTAs per SM x 100 %)
 int g_ablate = 0;
 int g_full_sm = 0;  // measurement hook: let one CTA use a whole SM's shared memory (deeper ring, one CTA per SM)
 
-// Ring depth: as many stages as fit in half of an SM's shared memory next to the
-// 64 KB of tables, so that two CTAs (of this kernel or of the next one in the
-// stream) are resident together.
+// Ring depth: as many slots as fit in half of an SM's shared memory next to the 64 KB of
+// tables, so that two CTAs (of this kernel or of the next one in the stream) are resident
+// together.  Block mode holds all slots of a unit at once (two for q = 4).
 
 int choose_stages(int q, int ncw, int smem_optin, int *smem_bytes) {
     const int sb = stage_bytes_for(q, ncw);
@@ -1256,8 +1309,9 @@ int choose_stages(int q, int ncw, int smem_optin, int *smem_bytes) {
     int stages = budget / sb;
     if (stages > 8) stages = 8;
     if (g_stage_override > 0 && g_stage_override < stages) stages = g_stage_override;
+    if (stages < q / planes_per_slot(q)) stages = q / planes_per_slot(q) <= budget / sb ? q / planes_per_slot(q) : 0;
     if (stages < 1) return 0;
-    *smem_bytes = LUT_BYTES + stages * sb + 2 * stages * 8 + 16;
+    *smem_bytes = LUT_BYTES + stages * sb + 2 * stages * 8 + 16;   // tables, ring, its barriers, a flag
     return stages;
 }
 
@@ -1280,11 +1334,12 @@ int encode_weight_map(CUtensorMap *out, const void *bw, int K, int N, int q) {
             return SAL_E_LAUNCH;
         g_encode_tiled = reinterpret_cast<TensorMapEncodeTiledFn>(fn);
     }
-    const cuuint64_t dims[2] = {(cuuint64_t)N, (cuuint64_t)(K / 32) * (cuuint64_t)q};
-    const cuuint64_t strides[1] = {(cuuint64_t)N * 4};  // bytes between rows; N % 4 == 0 keeps it a multiple of 16
-    const cuuint32_t box[2] = {(cuuint32_t)BOX_COLS, (cuuint32_t)(KB_WORDS * q)};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = g_encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(bw), dims, strides, box,
+    // [K/32 words][q planes][N columns], innermost first; strides in bytes of all but the innermost dimension
+    const cuuint64_t dims[3] = {(cuuint64_t)N, (cuuint64_t)q, (cuuint64_t)(K / 32)};
+    const cuuint64_t strides[2] = {(cuuint64_t)N * 4, (cuuint64_t)N * 4 * (cuuint64_t)q};  // N % 4 == 0 keeps them multiples of 16
+    const cuuint32_t box[3] = {(cuuint32_t)BOX_COLS, (cuuint32_t)planes_per_slot(q), (cuuint32_t)KB_WORDS};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = g_encode_tiled(out, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<void *>(bw), dims, strides, box,
                                       estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
                                       CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? SAL_OK : SAL_E_LAUNCH;
