@@ -555,6 +555,74 @@ def config5_record(args, timer, rank, world, device, peer_factory):
         del run, replay
     peak, _ = measured_peak()
     rec["roofline_frac_of_measured"] = round(rec["block_launches"]["value"] / world / peak, 4)
+    del lset, peer, y_full
+    torch.cuda.empty_cache()
+    if "decode" in args.legs:
+        rec["decoder"] = sharded_decoder_record(args, rank, world, device)
+    return rec
+
+
+def sharded_decoder_record(args, rank, world, device):
+    """tokens/s of the column-parallel decoder of the 70B architecture (80 blocks, hidden 8192, 64 query / 8 kv
+    heads, FFN 28672, BCQ 2 bit) at this number of GPUs: batch 1 (all-gather fused into the GEMV kernels) and 16
+    sequences in lock step (M = 16 products, NCCL all-gather), 128 new tokens after a 1024-token prompt.  Before
+    that, on a small shape, the column-parallel logits are compared with a single-GPU decoder of the same seed."""
+    import torch.distributed as dist
+
+    from shiftaddllm_b200 import decoder, shard_decoder
+
+    def max_over_ranks(v):
+        t = torch.tensor([v], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    rec = {"workload": "llama2-70b-shaped decoder, BCQ 2-bit g128 linears column-parallel over the GPUs, replicated attention / "
+                       "norms / fp16 lm_head, 1024-token prompt of uniform random ids, 128 greedy tokens, one CUDA graph per token",
+           "n_gpus": world}
+    # ---- correctness on a small shape: same model (same seed) on one GPU and column-parallel
+    small = decoder.LlamaShape(512, 2, 8, 8, 1024, vocab=1000)
+    par = shard_decoder.ColumnParallelDecoder(small, wbits=2, max_len=32, rank=rank, world=world, device=device, seed=9,
+                                              exchange=args.exchange)
+    one = decoder.BcqLlamaDecoder(small, wbits=2, max_len=32, device=device, seed=9, fused=True)
+    par.reset()
+    one.reset()
+    worst = 0.0
+    for t in (5, 17, 999, 3, 42):
+        par.token.fill_(t)
+        one.token.fill_(t)
+        par.step()
+        one.step()
+        torch.cuda.synchronize(device)
+        worst = max(worst, float((par.logits[0] - one.logits).abs().max() / one.logits.abs().max()))
+    rec["check_vs_single_gpu_decoder"] = {"max_rel_err_logits": round(max_over_ranks(worst), 6), "tolerance": 2e-2,
+                                          "shape": "hidden 512, 2 blocks, 8 heads, 8 kv heads, FFN 1024"}
+    del par, one
+    torch.cuda.empty_cache()
+    shape = decoder.SHAPES["llama2-70b"]
+    prompt, new = 1024, 128
+    for batch in (1, 16):
+        model = shard_decoder.ColumnParallelDecoder(shape, wbits=2, max_len=prompt + new + 16, batch=batch, rank=rank, world=world,
+                                                    device=device, seed=0, exchange=args.exchange)
+        if batch == 1:
+            r = shard_decoder.benchmark(model, prompt, new)
+            fill = "prompt fed through the model, one step per token"
+        else:
+            # the cache of the prompt positions is filled with synthetic values instead of 1024 model steps per
+            # sequence: the timed steps read the same number of cached positions either way
+            model.capture()
+            model.reset()
+            gen = torch.Generator(device=device).manual_seed(11)
+            model.k_cache[:, :, :prompt].copy_(0.5 * torch.randn(model.k_cache[:, :, :prompt].shape, device=device, generator=gen))
+            model.v_cache[:, :, :prompt].copy_(0.5 * torch.randn(model.v_cache[:, :, :prompt].shape, device=device, generator=gen))
+            model.pos.fill_(prompt)
+            r = shard_decoder.benchmark_steps(model, new)
+            fill = "cache of the prompt positions filled with synthetic values (same positions read per step)"
+        ms = max_over_ranks(r["ms_per_step"])
+        rec[f"batch{batch}"] = {"tokens_per_s": round(batch * 1e3 / ms, 1), "ms_per_step": round(ms, 4), "prompt": fill,
+                                "exchange": "fused into the GEMV kernels" if model.fused else ("NCCL all-gather" if world > 1 else "none")}
+        del model
+        torch.cuda.empty_cache()
     return rec
 
 

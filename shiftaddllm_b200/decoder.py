@@ -52,6 +52,7 @@ SHAPES = {
     "llama2-7b": LlamaShape(4096, 32, 32, 32, 11008),
     "llama2-70b": LlamaShape(8192, 80, 64, 8, 28672),
     "tiny": LlamaShape(256, 2, 4, 2, 512, vocab=1000),
+    "tiny4": LlamaShape(256, 2, 4, 4, 512, vocab=1000),    # four kv heads: splits over four ranks
 }
 
 
@@ -265,12 +266,72 @@ class BcqLlamaDecoder:
         self.k_cache.zero_()
         self.v_cache.zero_()
 
-    def feed(self, token_ids):
-        """Teacher-forced pass over a prompt (fills the KV cache), one graph replay per token."""
+    def feed(self, token_ids, chunk: int = 64):
+        """Teacher-forced pass over a prompt (fills the KV cache).  `chunk` > 1: the prompt goes through the
+        model in chunks of up to `chunk` (at most 64) tokens, every linear layer as ONE small-batch LUT product
+        per chunk — the way the reference feeds a prompt through the model's ordinary forward
+        (model/opt.py:397-411) — instead of one decode step per token.  `chunk` = 1: one step (graph replay)
+        per token."""
+        if chunk > 1 and len(token_ids) > 1:
+            return self.prefill(token_ids, chunk)
         run = self.graph.replay if self.graph is not None else self.step
         for t in token_ids:
             self.token.fill_(int(t))
             run()
+
+    def prefill(self, token_ids, chunk: int = 64):
+        """Chunked prompt pass: rows of a chunk share each weight stream (M = chunk rows per product,
+        2 <= M <= 64; a last chunk of one token runs the M = 1 kernel).  RMSNorm, RoPE and the causal attention
+        over the cache are torch ops here (a prompt is processed once; the per-token step is where the fused
+        helpers matter).  Leaves the cache, `pos`, the logits of the last prompt token and the greedy next token
+        exactly where a token-by-token `feed` would."""
+        s = self.shape
+        hd, kvh, rep, h = s.head_dim, s.kv_heads, s.heads // s.kv_heads, s.hidden
+        chunk = max(1, min(int(chunk), 64))
+        ids = torch.as_tensor(token_ids, dtype=torch.long, device=self.device).view(-1)
+        p0 = int(self.pos.item())
+        if p0 + ids.numel() > self.max_len:
+            raise ValueError("prompt does not fit the KV cache")
+        f16 = dict(dtype=torch.float16, device=self.device)
+        for c0 in range(0, ids.numel(), chunk):
+            tok = ids[c0:c0 + chunk]
+            m = tok.numel()
+            pos = torch.arange(p0 + c0, p0 + c0 + m, device=self.device)
+            total = p0 + c0 + m                                            # cached positions after this chunk
+            cos, sin = self.cos.index_select(0, pos)[:, None, :], self.sin.index_select(0, pos)[:, None, :]   # [m, 1, hd/2]
+
+            def rope(t, heads):
+                t = t.view(m, heads, 2, hd // 2).float()                   # rotate-half convention
+                a, b = t[:, :, 0, :], t[:, :, 1, :]
+                return torch.stack((a * cos - b * sin, b * cos + a * sin), dim=2).view(m, heads, hd).half()
+
+            causal = (torch.arange(total, device=self.device)[None, :] > pos[:, None]).view(1, m, 1, total)
+            x = self.embed.index_select(0, tok)                            # [m, hidden]
+            q, k, v = torch.empty(m, h, **f16), torch.empty(m, kvh * hd, **f16), torch.empty(m, kvh * hd, **f16)
+            o_out, down = torch.empty(m, h, **f16), torch.empty(m, h, **f16)
+            gate, up = torch.empty(m, s.ffn, **f16), torch.empty(m, s.ffn, **f16)
+            for li, blk in enumerate(self.blocks):
+                hn = F.rms_norm(x, (h,), blk.input_norm, s.eps)
+                _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (q, k, v))
+                qh, kh = rope(q, s.heads), rope(k, kvh)
+                self.k_cache[li].index_copy_(0, pos, kh)
+                self.v_cache[li].index_copy_(0, pos, v.view(m, kvh, hd))
+                keys = self.k_cache[li, :total].permute(1, 2, 0)           # [kvh, hd, T]
+                vals = self.v_cache[li, :total].permute(1, 0, 2)           # [kvh, T, hd]
+                scores = torch.matmul(qh.view(m, kvh, rep, hd).permute(1, 0, 2, 3), keys[:, None]).float() * (1.0 / math.sqrt(hd))
+                scores = scores.masked_fill(causal, float("-inf"))         # [kvh, m, rep, T]
+                attn = torch.matmul(torch.softmax(scores, dim=-1).half(), vals[:, None])       # [kvh, m, rep, hd]
+                attn = attn.permute(1, 0, 2, 3).reshape(m, h).contiguous()
+                _group((blk.o_proj,), attn, (o_out,))
+                x = x + o_out
+                hn = F.rms_norm(x, (h,), blk.post_norm, s.eps)
+                _group((blk.gate_proj, blk.up_proj), hn, (gate, up))
+                _group((blk.down_proj,), gate, (down,), x_mul=up)          # SiLU(gate)*up formed in the table build
+                x = x + down
+        hn = F.rms_norm(x[-1:], (h,), self.final_norm, s.eps)
+        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
+        self.token.copy_(self.logits.argmax().view(1))
+        self.pos.add_(ids.numel())
 
     def generate(self, n):
         run = self.graph.replay if self.graph is not None else self.step

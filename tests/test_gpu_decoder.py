@@ -263,6 +263,30 @@ def test_graph_replay_equals_eager():
     assert torch.equal(eager, replayed)            # deterministic kernels: identical greedy tokens
 
 
+@pytest.mark.parametrize("chunk", [64, 5])
+def test_chunked_prefill_matches_token_by_token(chunk):
+    """A prompt fed in chunks (every linear one small-batch product per chunk; 70 tokens = a chunk of 64 and one
+    of 6, or fourteen chunks of 5) leaves the same cache, logits and next token as one decode step per token."""
+    prompt = torch.randint(0, 1000, (70,), generator=torch.Generator().manual_seed(8)).tolist()
+    a = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=96, seed=6)
+    a.reset()
+    a.feed(prompt, chunk=1)
+    b = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=96, seed=6)
+    b.reset()
+    b.feed(prompt, chunk=chunk)
+    torch.cuda.synchronize()
+    assert int(a.pos) == int(b.pos) == 70
+    scale = float(a.k_cache.float().abs().max())
+    assert float((a.k_cache.float() - b.k_cache.float()).abs().max()) <= 2e-2 * scale
+    assert float((a.v_cache.float() - b.v_cache.float()).abs().max()) <= 2e-2 * float(a.v_cache.float().abs().max())
+    assert float((a.logits - b.logits).abs().max()) <= 3e-2 * float(a.logits.abs().max())
+    ref = reference_logits(a, prompt)
+    assert float((b.logits - ref).abs().max()) <= 3e-2 * float(ref.abs().max())
+    # decoding continues from the chunk-filled cache
+    tb = b.generate(4)
+    assert tb.shape == (4,) and int(b.pos) == 74
+
+
 def test_atomic_mode_tracks_the_deterministic_mode():
     """fp32-atomic accumulation only changes the summation order: greedy tokens over a short
     generation agree with the deterministic path, and the accumulators are left clean."""
