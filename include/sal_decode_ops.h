@@ -31,15 +31,16 @@ int sal_residual_rmsnorm_f16(const void *x, const void *delta, const void *weigh
 int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos, const void *sin, const int64_t *pos,
                           void *k_cache, void *v_cache, int heads, int kv_heads, int hd, int max_len, void *stream);
 
-/* Variants for products that ran with SAL_OUT_F32_ATOMIC (their outputs are fp32 accumulators).  Every
+/* Variants for products that ran with SAL_OUT_FIXED_ATOMIC (their outputs are 64-bit fixed-point accumulators,
+ * signed integers in units of 2**-32, see include/sal_lutgemm.h).  Every
  * accumulator element is rounded to fp16 when read — the value the fp16-output path would have stored — and
  * then set back to zero, so the buffer is ready for the same layer's product of the next token.
- * sal_residual_rmsnorm_f32acc: as sal_residual_rmsnorm_f16 with delta fp32 (may be NULL); additionally clears
+ * sal_residual_rmsnorm_fixedacc: as sal_residual_rmsnorm_f16 with delta an accumulator vector (may be NULL); additionally clears
  * zero_a[0..zero_a_n) and zero_b[0..zero_b_n) (accumulators, e.g. gate and up, whose reader was a GEMV).
- * sal_rope_kv_write_f32acc: as sal_rope_kv_write_f16 with q, k, v fp32; the rotated query goes to q_out (fp16). */
-int sal_residual_rmsnorm_f32acc(const void *x, void *delta_f32, const void *weight, void *out, void *x_out, int n,
+ * sal_rope_kv_write_fixedacc: as sal_rope_kv_write_f16 with q, k, v accumulator vectors; the rotated query goes to q_out (fp16). */
+int sal_residual_rmsnorm_fixedacc(const void *x, void *delta_acc, const void *weight, void *out, void *x_out, int n,
                                 float eps, void *zero_a, int zero_a_n, void *zero_b, int zero_b_n, void *stream);
-int sal_rope_kv_write_f32acc(void *q_f32, void *k_f32, void *v_f32, void *q_out, const void *cos, const void *sin,
+int sal_rope_kv_write_fixedacc(void *q_acc, void *k_acc, void *v_acc, void *q_out, const void *cos, const void *sin,
                              const int64_t *pos, void *k_cache, void *v_cache, int heads, int kv_heads, int hd,
                              int max_len, void *stream);
 
@@ -60,12 +61,12 @@ int sal_attention_decode_split_f16(const void *q, const void *k_cache, const voi
                                    size_t workspace_bytes, void *stream);
 
 /* Rotary step + cache write + split attention in ONE kernel (one launch less per decoder block).  q [heads][hd],
- * k_new / v_new [kv_heads][hd] are the un-rotated projections of the new token: fp16 (inputs_f32 = 0; q is
- * left as it is), or fp32 accumulators (inputs_f32 = 1) that are rounded to fp16 on read and cleared.  The
+ * k_new / v_new [kv_heads][hd] are the un-rotated projections of the new token: fp16 (inputs_fixed = 0; q is
+ * left as it is), or fixed-point accumulators (inputs_fixed = 1) that are rounded to fp16 on read and cleared.  The
  * rotated key and the value are stored at position *pos of the caches (nothing is stored if *pos is outside
  * 0..max_len-1) and attention runs over positions 0..*pos.  Same shape limits, scratch buffer and results as
  * sal_rope_kv_write_f16 followed by sal_attention_decode_split_f16. */
-int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_f32, const void *cos, const void *sin,
+int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_fixed, const void *cos, const void *sin,
                               const int64_t *pos, void *k_cache, void *v_cache, void *out, int heads, int kv_heads, int hd,
                               int max_len, float scale, void *workspace, size_t workspace_bytes, void *stream);
 

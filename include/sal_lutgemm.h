@@ -24,7 +24,8 @@
  * pre-load the bias there (lut_gemm/quant.py:46).  SAL_ACCUMULATE reproduces
  * that contract; without it the bias add is fused and y is overwritten.
  * Accumulation is fp32 and the split-K reduction order is fixed, so results
- * are deterministic (the reference accumulates in fp16 with atomics).
+ * are deterministic (the reference accumulates in fp16 with atomics); the
+ * accumulator outputs of SAL_OUT_FIXED_ATOMIC are deterministic too (integer sums).
  */
 #ifndef SAL_LUTGEMM_H
 #define SAL_LUTGEMM_H
@@ -54,14 +55,16 @@ extern "C" {
 #define SAL_PDL 2u         /* launch with programmatic dependent launch: the packed planes are
                               prefetched while the previous kernel of the stream drains */
 #define SAL_FORCE_GENERIC 4u /* use the shape-agnostic kernel even where the tiled one applies */
-#define SAL_OUT_F32_ATOMIC 8u /* y is FLOAT32 [N]: bias + product is ADDED to it with fp32 atomic adds (M = 1,
-                                 tiled shapes only).  This is the reference's own output contract — its kernels
-                                 atomicAdd into `output` (mv_fp16_bias.hpp:101) — carried out in fp32.  No
-                                 scratch and no split-K reduction tail, but the summation order is not fixed:
-                                 results can differ in the last fp32 bit from run to run.  The caller zeroes
-                                 (or pre-loads) y. */
-#define SAL_SWIGLU_F32 16u   /* with sal_problem.x_mul: x and x_mul are FLOAT32 (accumulators written with
-                                 SAL_OUT_F32_ATOMIC), rounded to fp16 before silu(x) * x_mul is formed */
+#define SAL_OUT_FIXED_ATOMIC 8u /* y is INT64 [N], a fixed-point accumulator in units of 2**-32: bias + product is ADDED
+                                  to it with 64-bit integer atomic adds (M = 1, tiled shapes only).  This is the
+                                  reference's own output contract — its kernels atomicAdd into `output`
+                                  (mv_fp16_bias.hpp:101) — carried out exactly: integer addition is associative, so the
+                                  accumulated value does not depend on the order in which the thread blocks arrive and
+                                  results are bit-identical from run to run.  Every partial sum is rounded once to
+                                  2**-32 (2.3e-10); |y| must stay below 2**31.  No scratch and no split-K reduction
+                                  tail.  The caller zeroes (or pre-loads) y; value = (double)y[n] * 2**-32. */
+#define SAL_SWIGLU_FIXED 16u   /* with sal_problem.x_mul: x and x_mul are such INT64 accumulators (written with
+                                  SAL_OUT_FIXED_ATOMIC), rounded to fp16 before silu(x) * x_mul is formed */
 
 #define SAL_MAX_Q 8
 #define SAL_MAX_M 64

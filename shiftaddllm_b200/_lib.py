@@ -17,7 +17,7 @@ LIB_PATH = os.environ.get("SAL_LUTGEMM_LIBRARY") or os.path.join(_PKG_DIR, "libs
 SAL_OK = 0
 SAL_E_NULL, SAL_E_SHAPE, SAL_E_ALIGN, SAL_E_WORKSPACE = -1, -2, -3, -4
 SAL_E_LAUNCH, SAL_E_UNSUPPORTED, SAL_E_DEVICE, SAL_E_TIMEOUT = -5, -6, -7, -8
-SAL_ACCUMULATE, SAL_PDL, SAL_FORCE_GENERIC, SAL_OUT_F32_ATOMIC, SAL_SWIGLU_F32 = 1, 2, 4, 8, 16
+SAL_ACCUMULATE, SAL_PDL, SAL_FORCE_GENERIC, SAL_OUT_FIXED_ATOMIC, SAL_SWIGLU_FIXED = 1, 2, 4, 8, 16
 SAL_MAX_GROUP = 8
 SAL_MAX_PEERS = 8
 SAL_MAX_M = 64
@@ -67,8 +67,8 @@ SIGNATURES = {
     # include/sal_decode_ops.h
     "sal_residual_rmsnorm_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _vp]),
     "sal_rope_kv_write_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
-    "sal_residual_rmsnorm_f32acc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _vp, _i, _vp, _i, _vp]),
-    "sal_rope_kv_write_f32acc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
+    "sal_residual_rmsnorm_fixedacc": (_i, [_vp, _vp, _vp, _vp, _vp, _i, ctypes.c_float, _vp, _i, _vp, _i, _vp]),
+    "sal_rope_kv_write_fixedacc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "sal_attention_decode_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp]),
     "sal_attention_workspace_bytes": (ctypes.c_size_t, [_i, _i]),
     "sal_attention_decode_split_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp, ctypes.c_size_t, _vp]),

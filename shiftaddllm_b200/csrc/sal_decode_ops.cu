@@ -9,6 +9,11 @@
 
 namespace {
 
+// Fixed-point accumulators written by SAL_OUT_FIXED_ATOMIC products: signed 64-bit integers in units of 2**-32.
+typedef long long acc_t;
+__device__ __forceinline__ float acc_value(acc_t v) { return __ll2float_rn(v) * 2.3283064365386963e-10f; }
+
+
 // Programmatic dependent launch: let the next kernel of the stream start (it may prefetch its
 // constant operands), then wait until the previous kernel's results are visible.
 __device__ __forceinline__ void pdl_prologue() {
@@ -110,12 +115,12 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_kernel(const __half *x,
     }
 }
 
-// fp32-accumulator variant: delta is an fp32 vector written by SAL_OUT_F32_ATOMIC products; it is rounded to
-// fp16 (what the fp16-output path would have stored), consumed, and zeroed for its next use, together with up
-// to two more accumulator vectors whose consumers (many CTAs of a GEMV) could not zero them themselves.
-__global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half *x, float *delta, const __half *w, __half *out,
-                                                                    __half *x_out, int n, float eps, float *zero_a, int zero_a_n,
-                                                                    float *zero_b, int zero_b_n) {
+// Accumulator variant: delta is a fixed-point accumulator vector written by SAL_OUT_FIXED_ATOMIC products; it is
+// rounded to fp16 (what the fp16-output path would have stored), consumed, and zeroed for its next use, together
+// with up to two more accumulator vectors whose consumers (many CTAs of a GEMV) could not zero them themselves.
+__global__ void __launch_bounds__(1024) residual_rmsnorm_acc_kernel(const __half *x, acc_t *delta, const __half *w, __half *out,
+                                                                    __half *x_out, int n, float eps, acc_t *zero_a, int zero_a_n,
+                                                                    acc_t *zero_b, int zero_b_n) {
     __shared__ float red[32];
     extern __shared__ float tbuf[];  // n floats
     pdl_prologue();
@@ -123,8 +128,8 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half
         // CTAs 1.. only clear the extra accumulators (hundreds of KB for an FFN-wide pair): nothing here depends
         // on the norm, so it runs beside it instead of in front of it
         const int stride = (gridDim.x - 1) * blockDim.x, first = (blockIdx.x - 1) * blockDim.x + threadIdx.x;
-        for (int i = first; i < zero_a_n; i += stride) zero_a[i] = 0.f;
-        for (int i = first; i < zero_b_n; i += stride) zero_b[i] = 0.f;
+        for (int i = first; i < zero_a_n; i += stride) zero_a[i] = 0;
+        for (int i = first; i < zero_b_n; i += stride) zero_b[i] = 0;
         return;
     }
     if (fast_rows_ok(n, x, delta, w, out, x_out)) {
@@ -135,14 +140,18 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half
         if (mine) {
             const uint4 xv = *reinterpret_cast<const uint4 *>(x + i);
             wv = *reinterpret_cast<const uint4 *>(w + i);
-            float4 d0 = make_float4(0.f, 0.f, 0.f, 0.f), d1 = d0;
+            float df[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             if (delta) {
-                d0 = *reinterpret_cast<const float4 *>(delta + i);
-                d1 = *reinterpret_cast<const float4 *>(delta + i + 4);
-                *reinterpret_cast<float4 *>(delta + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-                *reinterpret_cast<float4 *>(delta + i + 4) = make_float4(0.f, 0.f, 0.f, 0.f);
+                longlong2 d[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) d[k] = *reinterpret_cast<const longlong2 *>(delta + i + 2 * k);   // 16-byte loads, all in flight
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    *reinterpret_cast<longlong2 *>(delta + i + 2 * k) = make_longlong2(0, 0);
+                    df[2 * k] = acc_value(d[k].x);
+                    df[2 * k + 1] = acc_value(d[k].y);
+                }
             }
-            const float df[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
             const __half *xh = reinterpret_cast<const __half *>(&xv);
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
@@ -165,8 +174,8 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         float t = __half2float(x[i]);
         if (delta) {
-            t = __half2float(__float2half_rn(t + __half2float(__float2half_rn(delta[i]))));
-            delta[i] = 0.f;
+            t = __half2float(__float2half_rn(t + __half2float(__float2half_rn(acc_value(delta[i])))));
+            delta[i] = 0;
         }
         tbuf[i] = t;
         ss += t * t;
@@ -180,9 +189,9 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_f32_kernel(const __half
     }
 }
 
-// fp32-accumulator variant of the rotary step: q, k, v are fp32 accumulators (rounded to fp16 on read, then
+// Accumulator variant of the rotary step: q, k, v are fixed-point accumulators (rounded to fp16 on read, then
 // zeroed); the rotated query goes to q_out (fp16), rotated k and v to the caches.
-__global__ void rope_kv_write_f32_kernel(float *q, float *k, float *v, __half *q_out, const float *cos_t, const float *sin_t,
+__global__ void rope_kv_write_acc_kernel(acc_t *q, acc_t *k, acc_t *v, __half *q_out, const float *cos_t, const float *sin_t,
                                          const int64_t *pos_p, __half *k_cache, __half *v_cache, int heads, int kv_heads,
                                          int hd, int max_len) {
     pdl_prologue();
@@ -196,18 +205,19 @@ __global__ void rope_kv_write_f32_kernel(float *q, float *k, float *v, __half *q
         const int j = is_q ? idx : idx - nq;
         const int h = j / half, i = j % half;
         const float c = cos_t[pos * half + i], s = sin_t[pos * half + i];
-        float *src = is_q ? q : k;
-        const float a = __half2float(__float2half_rn(src[h * hd + i])), b = __half2float(__float2half_rn(src[h * hd + half + i]));
-        src[h * hd + i] = 0.f;
-        src[h * hd + half + i] = 0.f;
+        acc_t *src = is_q ? q : k;
+        const float a = __half2float(__float2half_rn(acc_value(src[h * hd + i])));
+        const float b = __half2float(__float2half_rn(acc_value(src[h * hd + half + i])));
+        src[h * hd + i] = 0;
+        src[h * hd + half + i] = 0;
         const __half ra = __float2half_rn(a * c - b * s), rb = __float2half_rn(b * c + a * s);
         __half *dst = is_q ? q_out : k_cache + ((size_t)pos * kv_heads) * hd;
         dst[h * hd + i] = ra;
         dst[h * hd + half + i] = rb;
     } else if (idx < nq + nk + nv) {
         const int j = idx - nq - nk;
-        v_cache[(size_t)pos * kv_heads * hd + j] = __float2half_rn(v[j]);
-        v[j] = 0.f;
+        v_cache[(size_t)pos * kv_heads * hd + j] = __float2half_rn(acc_value(v[j]));
+        v[j] = 0;
     }
 }
 
@@ -374,15 +384,15 @@ constexpr int ATTN_WARPS = 8;
 // ROPE: the rotary step of the new token is done here instead of by a kernel of its own.  q is the
 // un-rotated query (rotated while it is loaded); the CTA whose slice holds position *pos rotates the new
 // key, writes it and the new value into the caches and then reads them back like any other row.
-// ROPE = 2: q, k_new, v_new are fp32 accumulators, rounded to fp16 on read and cleared afterwards (k, v by
+// ROPE = 2: q, k_new, v_new are fixed-point accumulators, rounded to fp16 on read and cleared afterwards (k, v by
 // the CTA that consumed them; q by the CTA that merges, i.e. after every CTA of the kv head has read it).
 struct RopeArgs {
-    void *k_new, *v_new;       // [kv_heads][hd], fp16 (ROPE 1) or fp32 (ROPE 2)
+    void *k_new, *v_new;       // [kv_heads][hd], fp16 (ROPE 1) or fixed-point accumulators (ROPE 2)
     const float *cos_t, *sin_t;  // [max_len][hd / 2]
 };
 template <int ROPE>
 __device__ __forceinline__ float rope_in(const void *p, size_t i) {
-    if (ROPE == 2) return __half2float(__float2half_rn(reinterpret_cast<const float *>(p)[i]));
+    if (ROPE == 2) return __half2float(__float2half_rn(acc_value(reinterpret_cast<const acc_t *>(p)[i])));
     return __half2float(reinterpret_cast<const __half *>(p)[i]);
 }
 
@@ -442,8 +452,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
             for (int j = tid; j < hd; j += blockDim.x) {
                 vrow[j] = __float2half_rn(rope_in<ROPE>(ra.v_new, (size_t)kvh * hd + j));
                 if (ROPE == 2) {
-                    reinterpret_cast<float *>(ra.k_new)[(size_t)kvh * hd + j] = 0.f;
-                    reinterpret_cast<float *>(ra.v_new)[(size_t)kvh * hd + j] = 0.f;
+                    reinterpret_cast<acc_t *>(ra.k_new)[(size_t)kvh * hd + j] = 0;
+                    reinterpret_cast<acc_t *>(ra.v_new)[(size_t)kvh * hd + j] = 0;
                 }
             }
         }
@@ -635,8 +645,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
         out[((size_t)kvh * G + g) * hd + d] = __float2half_rn(acc);
     }
     if (ROPE == 2) {   // every CTA of this kv head has arrived, hence has read the query accumulators
-        float *q32 = reinterpret_cast<float *>(const_cast<void *>(q));
-        for (int i = tid; i < G * hd; i += blockDim.x) q32[(size_t)kvh * G * hd + i] = 0.f;
+        acc_t *qacc = reinterpret_cast<acc_t *>(const_cast<void *>(q));
+        for (int i = tid; i < G * hd; i += blockDim.x) qacc[(size_t)kvh * G * hd + i] = 0;
     }
     if (tid == 0) counters[kvh] = 0u;   // ready for the next call
 }
@@ -735,7 +745,7 @@ int sal_rope_kv_write_f16(void *q, const void *k, const void *v, const void *cos
                       reinterpret_cast<__half *>(k_cache), reinterpret_cast<__half *>(v_cache), heads, kv_heads, hd, max_len);
 }
 
-int sal_residual_rmsnorm_f32acc(const void *x, void *delta_f32, const void *weight, void *out, void *x_out, int n, float eps,
+int sal_residual_rmsnorm_fixedacc(const void *x, void *delta_acc, const void *weight, void *out, void *x_out, int n, float eps,
                                 void *zero_a, int zero_a_n, void *zero_b, int zero_b_n, void *stream) {
     if (!x || !weight || !out) return SAL_E_NULL;
     if (n < 1 || n > 12000 /* the row is staged in shared memory, 48 KB with the reduction scratch */ || zero_a_n < 0 || zero_b_n < 0 || (zero_a_n && !zero_a) || (zero_b_n && !zero_b)) return SAL_E_SHAPE;
@@ -743,20 +753,20 @@ int sal_residual_rmsnorm_f32acc(const void *x, void *delta_f32, const void *weig
     // one CTA for the norm, plus one per 16 K extra accumulator words to clear (at most 32)
     int zero_ctas = (zero_a_n + zero_b_n + 16383) / 16384;
     if (zero_ctas > 32) zero_ctas = 32;
-    return launch_pdl(residual_rmsnorm_f32_kernel, dim3(1 + zero_ctas), dim3(threads), (size_t)n * sizeof(float), stream,
-                      reinterpret_cast<const __half *>(x), reinterpret_cast<float *>(delta_f32),
+    return launch_pdl(residual_rmsnorm_acc_kernel, dim3(1 + zero_ctas), dim3(threads), (size_t)n * sizeof(float), stream,
+                      reinterpret_cast<const __half *>(x), reinterpret_cast<acc_t *>(delta_acc),
                       reinterpret_cast<const __half *>(weight), reinterpret_cast<__half *>(out), reinterpret_cast<__half *>(x_out),
-                      n, eps, reinterpret_cast<float *>(zero_a), zero_a_n, reinterpret_cast<float *>(zero_b), zero_b_n);
+                      n, eps, reinterpret_cast<acc_t *>(zero_a), zero_a_n, reinterpret_cast<acc_t *>(zero_b), zero_b_n);
 }
 
-int sal_rope_kv_write_f32acc(void *q_f32, void *k_f32, void *v_f32, void *q_out, const void *cos, const void *sin,
+int sal_rope_kv_write_fixedacc(void *q_acc, void *k_acc, void *v_acc, void *q_out, const void *cos, const void *sin,
                              const int64_t *pos, void *k_cache, void *v_cache, int heads, int kv_heads, int hd, int max_len,
                              void *stream) {
-    if (!q_f32 || !k_f32 || !v_f32 || !q_out || !cos || !sin || !pos || !k_cache || !v_cache) return SAL_E_NULL;
+    if (!q_acc || !k_acc || !v_acc || !q_out || !cos || !sin || !pos || !k_cache || !v_cache) return SAL_E_NULL;
     if (heads < 1 || kv_heads < 1 || hd < 2 || (hd & 1) || max_len < 1) return SAL_E_SHAPE;
     const int total = heads * (hd / 2) + kv_heads * (hd / 2) + kv_heads * hd;
-    return launch_pdl(rope_kv_write_f32_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, reinterpret_cast<float *>(q_f32),
-                      reinterpret_cast<float *>(k_f32), reinterpret_cast<float *>(v_f32), reinterpret_cast<__half *>(q_out),
+    return launch_pdl(rope_kv_write_acc_kernel, dim3((total + 255) / 256), dim3(256), 0, stream, reinterpret_cast<acc_t *>(q_acc),
+                      reinterpret_cast<acc_t *>(k_acc), reinterpret_cast<acc_t *>(v_acc), reinterpret_cast<__half *>(q_out),
                       reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin), pos,
                       reinterpret_cast<__half *>(k_cache), reinterpret_cast<__half *>(v_cache), heads, kv_heads, hd, max_len);
 }
@@ -794,12 +804,12 @@ int sal_attention_decode_split_f16(const void *q, const void *k_cache, const voi
                                     RopeArgs{}, stream);
 }
 
-int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_f32, const void *cos, const void *sin,
+int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_fixed, const void *cos, const void *sin,
                               const int64_t *pos, void *k_cache, void *v_cache, void *out, int heads, int kv_heads, int hd,
                               int max_len, float scale, void *workspace, size_t workspace_bytes, void *stream) {
     if (!k_new || !v_new || !cos || !sin) return SAL_E_NULL;
     const RopeArgs ra = {k_new, v_new, reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin)};
-    return inputs_f32 ? attention_split_entry<2>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace,
+    return inputs_fixed ? attention_split_entry<2>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace,
                                                  workspace_bytes, ra, stream)
                       : attention_split_entry<1>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace,
                                                  workspace_bytes, ra, stream);

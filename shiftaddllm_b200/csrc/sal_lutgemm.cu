@@ -174,6 +174,13 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t select
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
     return d;
 }
+// Fixed-point accumulators (SAL_OUT_FIXED_ATOMIC): signed 64-bit integers counting units of 2**-32.  Integer
+// addition is associative, so the value left by any number of atomic adds does not depend on their order.
+constexpr float SAL_FIXED_ONE = 4294967296.f;            // 2**32
+constexpr float SAL_FIXED_INV = 2.3283064365386963e-10f; // 2**-32
+__device__ __forceinline__ unsigned long long to_fixed(float v) { return (unsigned long long)__float2ll_rn(v * SAL_FIXED_ONE); }
+__device__ __forceinline__ float from_fixed(long long v) { return __ll2float_rn(v) * SAL_FIXED_INV; }
+
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
@@ -238,18 +245,21 @@ __device__ __forceinline__ void build_tables_impl(const __half *__restrict__ x0,
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
         if (SWIGLU == 2) {
-            // gate and up are the fp32 accumulators two earlier products added into (plain loads: they were
+            // gate and up are the fixed-point accumulators two earlier products added into (plain loads: they were
             // written by atomics of the previous kernels, not constant data)
-            const float4 *gp = reinterpret_cast<const float4 *>(r == 0 ? x0 : x1) + 2 * lane;
-            const float4 *up = reinterpret_cast<const float4 *>(r == 0 ? m0 : m1) + 2 * lane;
-            const float4 g0 = gp[0], g1 = gp[1], u0 = up[0], u1 = up[1];
-            const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-            const float u[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+            const longlong2 *gp = reinterpret_cast<const longlong2 *>(r == 0 ? x0 : x1) + 4 * lane;
+            const longlong2 *up = reinterpret_cast<const longlong2 *>(r == 0 ? m0 : m1) + 4 * lane;
+            long long g[8], u[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const longlong2 gv = gp[i], uv = up[i];
+                g[2 * i] = gv.x, g[2 * i + 1] = gv.y, u[2 * i] = uv.x, u[2 * i + 1] = uv.y;
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float gi = __half2float(__float2half_rn(g[i]));   // the two-step path rounds gate and up to fp16 first
+                const float gi = __half2float(__float2half_rn(from_fixed(g[i])));   // the two-step path rounds gate and up to fp16 first
                 const float sg = __half2float(__float2half_rn(gi / (1.f + __expf(-gi))));
-                xf[r][i] = __half2float(__float2half_rn(sg * __half2float(__float2half_rn(u[i]))));
+                xf[r][i] = __half2float(__float2half_rn(sg * __half2float(__float2half_rn(from_fixed(u[i])))));
             }
             continue;
         }
@@ -307,12 +317,18 @@ __device__ __forceinline__ void push_to_peers(const ExchangeParams &ex, long lon
     const long long off = gather_off + (long long)ex.rank * N + n;
     for (int t = 0; t < ex.world; ++t) ex.base[t][off] = v;  // includes this rank's own gather buffer
 }
-// After all threads of a writer CTA pushed their elements: make the stores visible system-wide,
-// then bump this launch's counter on every peer (and on this rank).  One arrival per writer CTA.
+// After all threads of a writer CTA pushed their elements: one CTA barrier, then ONE thread per peer publishes
+// them with a system-scope release add on that peer's counter of this launch (and on this rank's own).  The
+// release is cumulative: the pushes of the other threads happen before it through the barrier, so an acquire
+// load that sees the count also sees the data.  (A __threadfence_system() in each of the 256 threads before
+// the barrier, as an earlier version had, made every thread wait for the NVLink round trip of its own
+// stores.)  One arrival per writer CTA.
 __device__ __forceinline__ void signal_peers(const ExchangeParams &ex, int tid, int nthreads) {
-    __threadfence_system();
     consumer_barrier(nthreads);
-    if (tid < ex.world) atomicAdd_system(ex.flags[tid] + ex.slot, 1u);
+    if (tid < ex.world) {
+        unsigned *flag = ex.flags[tid] + ex.slot;
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(flag) : "memory");
+    }
 }
 
 // Fused exchange, consumer side: waits (bounded, ~1 s) until `expected` writer CTAs of all ranks
@@ -348,9 +364,9 @@ constexpr uint32_t SMEM_DYNAMIC_BASE = 1024;
 // rows; the same weight tile serves both rows through half2 table entries.  SWIGLU: the activation
 // is silu(x) * x_mul, formed while the tables are built (a separate instantiation, so that the
 // extra registers of that prologue do not weigh on the ordinary kernel).  EXCH: the fused all-gather
-// epilogue (peer stores + counters), likewise its own instantiation.  SWIGLU = 2: gate and up are fp32.
-// ATOMIC: y is an fp32 accumulator [N]; every CTA adds its partial sums with fp32 atomics (no scratch,
-// no reduction tail; the summation order is not fixed).
+// epilogue (peer stores + counters), likewise its own instantiation.  SWIGLU = 2: gate and up are such fixed-point accumulators.
+// ATOMIC: y is a 64-bit fixed-point accumulator [N] (units of 2**-32); every CTA adds its partial sums with
+// integer atomics (no scratch, no reduction tail; integer sums do not depend on the order of arrival).
 // BLK: block mode.  Every lookup has its own multiplier alpha[chunk][plane][column / gs].  The multipliers
 // of a tile (32 chunks x Q planes x up to 16 column groups) are fetched one tile ahead, decoded to fp32
 // and parked in the upper 128 bytes of the table rows (this mode keeps ONE set of tables, in the lower
@@ -457,9 +473,9 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     auto build_block = [&](int kb, int half, int w, auto nwarps_tag) {
         constexpr int NW = decltype(nwarps_tag)::value;
         const size_t ko = (size_t)kb * KB_FEATS;
-        if (SWIGLU == 2) {   // fp32 operands: same element offsets, twice the bytes (pointers are carried as __half*)
-            const __half *g32 = pr.x + 2 * ((xrow0 - pr.x) + ko);
-            const __half *u32 = pr.x_mul + 2 * ((xrow0 - pr.x) + ko);
+        if (SWIGLU == 2) {   // 64-bit fixed-point operands: same element offsets, four times the bytes (pointers are carried as __half*)
+            const __half *g32 = pr.x + 4 * ((xrow0 - pr.x) + ko);
+            const __half *u32 = pr.x_mul + 4 * ((xrow0 - pr.x) + ko);
             build_tables_impl<NW, ROWS, SWIGLU>(g32, g32, u32, u32, lut_s + half * 128, w, lane);
         } else {
             // x_mul row = x_mul + (the same element offset the x row has)
@@ -839,8 +855,9 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
 
     // ---------------------------------- epilogue ----------------------------------
     if (ATOMIC) {
-        // y is an fp32 accumulator: fire-and-forget reductions in L2, nothing to wait for
-        float *yacc = reinterpret_cast<float *>(pr.y);
+        // y is a 64-bit fixed-point accumulator: fire-and-forget integer reductions in L2, nothing to wait for, and
+        // the sum does not depend on the order in which the CTAs arrive
+        unsigned long long *yacc = reinterpret_cast<unsigned long long *>(pr.y);
 #pragma unroll
         for (int sub = 0; sub < MAX_SUB; ++sub) {
             const int n = (sub_begin + sub) * CW + col;
@@ -848,7 +865,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             if (sub < nsub && n < N && touched) {
                 float v = acc[0][sub];
                 if (pr.bias && u_begin <= sub && sub < u_end) v += __half2float(pr.bias[n]);  // the CTA holding unit (K block 0, sub)
-                atomicAdd(yacc + n, v);
+                atomicAdd(yacc + n, to_fixed(v));
             }
         }
         return;
@@ -1505,8 +1522,8 @@ int build_tiled_group(const sal_problem *problems, int count, unsigned flags, bo
     L.row_groups = (M + L.rows - 1) / L.rows;
     const int ncw = 8;   // consumer warps per CTA (a 16-warp, one-CTA-per-SM shape was measured and is not faster)
     // all problems of a launch must agree on the activation form
-    L.atomic_out = (flags & SAL_OUT_F32_ATOMIC) != 0;
-    L.swiglu = problems[0].x_mul == nullptr ? 0 : ((flags & SAL_SWIGLU_F32) ? 2 : 1);
+    L.atomic_out = (flags & SAL_OUT_FIXED_ATOMIC) != 0;
+    L.swiglu = problems[0].x_mul == nullptr ? 0 : ((flags & SAL_SWIGLU_FIXED) ? 2 : 1);
     if ((L.atomic_out || L.swiglu == 2) && (M != 1 || ex)) return SAL_E_UNSUPPORTED;
     if (blk && (L.atomic_out || L.swiglu || ex || count != 1)) return SAL_E_UNSUPPORTED;
     const int cw = ncw * 32;
@@ -1797,7 +1814,7 @@ int sal_lutgemv_shift_scale(const void *bw, const void *alpha, const void *bias,
         rc = run_tiled_group(&sp, 1, flags, workspace, workspace_bytes, s, nullptr);
         // a scratch buffer that is too small for this shape (or more row pairs x column ranges than it has
         // arrival counters) is not an error for the reference-style call: the generic kernel takes it
-        if (rc != SAL_E_WORKSPACE || (flags & (SAL_OUT_F32_ATOMIC | SAL_SWIGLU_F32))) return rc;
+        if (rc != SAL_E_WORKSPACE || (flags & (SAL_OUT_FIXED_ATOMIC | SAL_SWIGLU_FIXED))) return rc;
     }
     GenericParams p = {};
     p.bw = reinterpret_cast<const uint32_t *>(bw);

@@ -27,22 +27,22 @@ def rope_kv_write(q, k, v, cos, sin, pos, k_cache, v_cache, heads, kv_heads, hd)
                                          k_cache.shape[0], _stream(q)), "sal_rope_kv_write_f16")
 
 
-def residual_rmsnorm_f32acc(x, delta32, weight, out, x_out, eps: float, zero_a=None, zero_b=None):
-    """As residual_rmsnorm with an fp32 accumulator as delta (consumed and zeroed); zero_a / zero_b:
-    further fp32 accumulators to clear."""
+def residual_rmsnorm_fixedacc(x, delta32, weight, out, x_out, eps: float, zero_a=None, zero_b=None):
+    """As residual_rmsnorm with an int64 fixed-point accumulator as delta (consumed and zeroed); zero_a / zero_b:
+    further accumulators to clear."""
     lib = _lib.load()
-    _lib.check(lib.sal_residual_rmsnorm_f32acc(x.data_ptr(), None if delta32 is None else delta32.data_ptr(), weight.data_ptr(),
+    _lib.check(lib.sal_residual_rmsnorm_fixedacc(x.data_ptr(), None if delta32 is None else delta32.data_ptr(), weight.data_ptr(),
                                                out.data_ptr(), None if x_out is None else x_out.data_ptr(), x.numel(), float(eps),
                                                None if zero_a is None else zero_a.data_ptr(), 0 if zero_a is None else zero_a.numel(),
                                                None if zero_b is None else zero_b.data_ptr(), 0 if zero_b is None else zero_b.numel(),
-                                               _stream(x)), "sal_residual_rmsnorm_f32acc")
+                                               _stream(x)), "sal_residual_rmsnorm_fixedacc")
 
 
-def rope_kv_write_f32acc(q32, k32, v32, q_out, cos, sin, pos, k_cache, v_cache, heads, kv_heads, hd):
+def rope_kv_write_fixedacc(q32, k32, v32, q_out, cos, sin, pos, k_cache, v_cache, heads, kv_heads, hd):
     lib = _lib.load()
-    _lib.check(lib.sal_rope_kv_write_f32acc(q32.data_ptr(), k32.data_ptr(), v32.data_ptr(), q_out.data_ptr(), cos.data_ptr(),
+    _lib.check(lib.sal_rope_kv_write_fixedacc(q32.data_ptr(), k32.data_ptr(), v32.data_ptr(), q_out.data_ptr(), cos.data_ptr(),
                                             sin.data_ptr(), pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), heads,
-                                            kv_heads, hd, k_cache.shape[0], _stream(q_out)), "sal_rope_kv_write_f32acc")
+                                            kv_heads, hd, k_cache.shape[0], _stream(q_out)), "sal_rope_kv_write_fixedacc")
 
 
 def attention_workspace(heads: int, hd: int, device) -> torch.Tensor:
@@ -70,12 +70,12 @@ def attention_decode(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, scale: 
 
 def rope_attention_decode(q, k_new, v_new, cos, sin, pos, k_cache, v_cache, out, heads, kv_heads, hd, scale: float, workspace):
     """Rotary step of the new token, cache write and split attention in one kernel.  q / k_new / v_new: fp16
-    projections (left untouched) or fp32 accumulators (consumed and cleared).  Returns False — having done
+    projections (left untouched) or int64 fixed-point accumulators (consumed and cleared).  Returns False — having done
     nothing — for shapes the split kernel does not take."""
     lib = _lib.load()
-    f32 = q.dtype == torch.float32
-    if k_new.dtype != q.dtype or v_new.dtype != q.dtype or q.dtype not in (torch.float16, torch.float32):
-        raise RuntimeError("q, k_new and v_new must all be float16 or all float32")
+    f32 = q.dtype == torch.int64          # fixed-point accumulators (consumed and cleared)
+    if k_new.dtype != q.dtype or v_new.dtype != q.dtype or q.dtype not in (torch.float16, torch.int64):
+        raise RuntimeError("q, k_new and v_new must all be float16 or all int64 fixed-point accumulators")
     rc = lib.sal_rope_attention_decode(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), 1 if f32 else 0, cos.data_ptr(),
                                        sin.data_ptr(), pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
                                        heads, kv_heads, hd, k_cache.shape[0], float(scale), workspace.data_ptr(),

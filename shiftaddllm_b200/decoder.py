@@ -78,12 +78,12 @@ class _Block:
                 "gate_proj": self.gate_proj, "up_proj": self.up_proj, "down_proj": self.down_proj}
 
 
-def _group(lins, x, outs, pdl=True, x_mul=None, atomic=False, swiglu_f32=False):
+def _group(lins, x, outs, pdl=True, x_mul=None, atomic=False, swiglu_fixed=False):
     """One grouped LUT-GEMV launch: every layer of `lins` applied to the same activation row
     (`x_mul` given: to silu(x) * x_mul, formed inside the kernel)."""
     probs = [dict(output=o, bWeight=l.binaryWeight, alpha=l.alpha, bias=l.bias, d_input=x, mSize=l.N, kSize=l.K,
                   nb=l.wbit, num_groups=l.alpha.shape[0], d_input_mul=x_mul) for l, o in zip(lins, outs)]
-    lutgemm.lutgemv_grouped(probs, pdl=pdl, atomic_f32=atomic, swiglu_f32=swiglu_f32)
+    lutgemm.lutgemv_grouped(probs, pdl=pdl, atomic_fixed=atomic, swiglu_fixed=swiglu_fixed)
 
 
 class BcqLlamaDecoder:
@@ -93,8 +93,9 @@ class BcqLlamaDecoder:
                  seed: int = 0, fused: bool = True, atomic: bool = False):
         self.shape, self.max_len = shape, max_len
         self.fused = fused   # fused CUDA helpers between the GEMVs (False: plain torch ops)
-        # atomic: the GEMVs add into fp32 accumulators with atomics (no split-K reduction tail, summation
-        # order not fixed) and the helpers consume and clear those accumulators; implies fused
+        # atomic: the GEMVs add into 64-bit fixed-point accumulators with integer atomics (no split-K reduction
+        # tail; integer sums do not depend on the order of arrival, so still deterministic) and the helpers
+        # consume and clear those accumulators; implies fused
         self.atomic = atomic
         self.device = torch.device(device)
         gen = torch.Generator(device=self.device).manual_seed(1000003 * seed + 5)
@@ -120,11 +121,11 @@ class BcqLlamaDecoder:
         self._down = torch.empty(1, h, **f16)
         self._x, self._hn = torch.empty(1, h, **f16), torch.empty(1, h, **f16)
         self._attn, self._act = torch.empty(1, h, **f16), torch.empty(1, shape.ffn, **f16)
-        # fp32 accumulators of the atomic mode (small; always present so that the mode can be switched later)
-        f32 = dict(dtype=torch.float32, device=self.device)
-        self._q32, self._k32, self._v32 = torch.zeros(1, h, **f32), torch.zeros(1, kvh * hd, **f32), torch.zeros(1, kvh * hd, **f32)
-        self._o32, self._down32 = torch.zeros(1, h, **f32), torch.zeros(1, h, **f32)
-        self._gate32, self._up32 = torch.zeros(1, shape.ffn, **f32), torch.zeros(1, shape.ffn, **f32)
+        # fixed-point accumulators of the atomic mode (small; always present so that the mode can be switched later)
+        f32 = dict(dtype=torch.int64, device=self.device)   # fixed-point accumulators, units of 2**-32
+        self._qacc, self._kacc, self._vacc = torch.zeros(1, h, **f32), torch.zeros(1, kvh * hd, **f32), torch.zeros(1, kvh * hd, **f32)
+        self._oacc, self._downacc = torch.zeros(1, h, **f32), torch.zeros(1, h, **f32)
+        self._gateacc, self._upacc = torch.zeros(1, shape.ffn, **f32), torch.zeros(1, shape.ffn, **f32)
         self._attn_ws = decode_ops.attention_workspace(shape.heads, hd, self.device) if fused else None
         self._rope_fused = True   # rotary step inside the attention kernel (set False to run it as a kernel of its own)
         self.graph = None
@@ -204,14 +205,14 @@ class BcqLlamaDecoder:
         self.pos.add_(1)
 
     def set_atomic(self, atomic: bool):
-        """Switches between fixed-order fp16 outputs and fp32 atomic accumulation (drops a captured graph)."""
+        """Switches between fp16 outputs reduced in fixed order and fixed-point atomic accumulation (drops a captured graph)."""
         self.atomic = bool(atomic)
         self.graph = None
-        for buf in (self._q32, self._k32, self._v32, self._o32, self._down32, self._gate32, self._up32):
+        for buf in (self._qacc, self._kacc, self._vacc, self._oacc, self._downacc, self._gateacc, self._upacc):
             buf.zero_()
 
     def _step_atomic(self):
-        """The fused step with fp32 atomic accumulation: every GEMV adds into an fp32 buffer that starts at
+        """The fused step with fixed-point atomic accumulation: every GEMV adds into an int64 buffer that starts at
         zero, the helper that consumes a buffer rounds it to fp16 and clears it again (gate/up, whose reader
         is the down projection itself, are cleared by the next residual+RMSNorm)."""
         s = self.shape
@@ -221,22 +222,22 @@ class BcqLlamaDecoder:
         torch.index_select(self.embed, 0, self.token, out=x)
         delta = None
         for li, blk in enumerate(self.blocks):
-            pend = (self._gate32, self._up32) if li > 0 else (None, None)
-            decode_ops.residual_rmsnorm_f32acc(x, delta, blk.input_norm, hn, x, s.eps, *pend)
-            _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q32, self._k32, self._v32), atomic=True)
+            pend = (self._gateacc, self._upacc) if li > 0 else (None, None)
+            decode_ops.residual_rmsnorm_fixedacc(x, delta, blk.input_norm, hn, x, s.eps, *pend)
+            _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._qacc, self._kacc, self._vacc), atomic=True)
             if not (self._rope_fused and decode_ops.rope_attention_decode(
-                    self._q32, self._k32, self._v32, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li],
+                    self._qacc, self._kacc, self._vacc, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li],
                     self._attn, s.heads, kvh, hd, scale, self._attn_ws)):
-                decode_ops.rope_kv_write_f32acc(self._q32, self._k32, self._v32, self._q, self.cos, self.sin, self.pos,
+                decode_ops.rope_kv_write_fixedacc(self._qacc, self._kacc, self._vacc, self._q, self.cos, self.sin, self.pos,
                                                 self.k_cache[li], self.v_cache[li], s.heads, kvh, hd)
                 decode_ops.attention_decode(self._q, self.k_cache[li], self.v_cache[li], self.pos, self._attn, s.heads, kvh, hd,
                                             scale, self._attn_ws)
-            _group((blk.o_proj,), self._attn, (self._o32,), atomic=True)
-            decode_ops.residual_rmsnorm_f32acc(x, self._o32, blk.post_norm, hn, x, s.eps)
-            _group((blk.gate_proj, blk.up_proj), hn, (self._gate32, self._up32), atomic=True)
-            _group((blk.down_proj,), self._gate32, (self._down32,), x_mul=self._up32, atomic=True, swiglu_f32=True)
-            delta = self._down32
-        decode_ops.residual_rmsnorm_f32acc(x, delta, self.final_norm, hn, x, s.eps, self._gate32, self._up32)
+            _group((blk.o_proj,), self._attn, (self._oacc,), atomic=True)
+            decode_ops.residual_rmsnorm_fixedacc(x, self._oacc, blk.post_norm, hn, x, s.eps)
+            _group((blk.gate_proj, blk.up_proj), hn, (self._gateacc, self._upacc), atomic=True)
+            _group((blk.down_proj,), self._gateacc, (self._downacc,), x_mul=self._upacc, atomic=True, swiglu_fixed=True)
+            delta = self._downacc
+        decode_ops.residual_rmsnorm_fixedacc(x, delta, self.final_norm, hn, x, s.eps, self._gateacc, self._upacc)
         self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
         self.token.copy_(self.logits.argmax().view(1))
         self.pos.add_(1)
@@ -503,7 +504,7 @@ def main():
     ap.add_argument("--prompt", type=int, default=512)
     ap.add_argument("--new", type=int, default=128)
     ap.add_argument("--no-fused", action="store_true", help="plain torch ops between the GEMVs")
-    ap.add_argument("--atomic", action="store_true", help="GEMVs accumulate into fp32 buffers with atomics (no split-K tail)")
+    ap.add_argument("--atomic", action="store_true", help="GEMVs accumulate into fixed-point buffers with integer atomics (no split-K tail, still deterministic)")
     ap.add_argument("--batch", type=int, default=1, help="sequences decoded in lock step (small-batch LUT products)")
     args = ap.parse_args()
     shape = SHAPES[args.model]
@@ -516,7 +517,7 @@ def main():
     model = BcqLlamaDecoder(shape, args.wbits, args.groupsize, max_len=args.prompt + 2 * args.new + 16, fused=not args.no_fused,
                             atomic=args.atomic)
     res = benchmark(model, args.prompt, args.new)
-    res.update({"atomic_f32_outputs": args.atomic, "fused_helpers": not args.no_fused, "model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompt"})
+    res.update({"atomic_fixed_outputs": args.atomic, "fused_helpers": not args.no_fused, "model": args.model, "wbits": args.wbits, "groupsize": args.groupsize, "data": "synthetic weights and prompt"})
     print(json.dumps(res))
 
 

@@ -21,6 +21,8 @@ import torch
 
 from . import _lib
 
+FIXED_ONE = float(2 ** 32)   # value of 1.0 in a fixed-point accumulator (SAL_OUT_FIXED_ATOMIC)
+
 _workspaces: dict = {}
 _superseded: list = []   # outgrown scratch buffers: kept alive, a CUDA graph captured earlier may still name them
 
@@ -163,14 +165,14 @@ def lutgemm_block_fused(output, bWeight, alpha, bias, d_input, mSize, kSize, nb,
         raise RuntimeError(f"unsupported alpha dtype {alpha.dtype}")
 
 
-def marshal_problems(problems, *, atomic_f32=False, swiglu_f32=False):
+def marshal_problems(problems, *, atomic_fixed=False, swiglu_fixed=False):
     """Checks the tensors of a grouped launch and returns (ctypes array, tensors to keep alive)."""
     if not 1 <= len(problems) <= _lib.SAL_MAX_GROUP:
         raise RuntimeError(f"a grouped launch takes 1..{_lib.SAL_MAX_GROUP} problems")
     arr = (_lib.SalProblem * len(problems))()
     keep = []
-    out_dtype = torch.float32 if atomic_f32 else torch.float16
-    in_dtype = torch.float32 if swiglu_f32 else torch.float16
+    out_dtype = torch.int64 if atomic_fixed else torch.float16     # fixed-point accumulators: int64, units of 2**-32
+    in_dtype = torch.int64 if swiglu_fixed else torch.float16
     for i, p in enumerate(problems):
         _req(p["output"], out_dtype, "output")
         _req(p["bWeight"], torch.int32, "bWeight")
@@ -199,14 +201,14 @@ class GroupedLaunch:
     storage must stay where it is.  Problems may differ in ``nb`` (mixed precision): the launch is
     then one kernel per distinct plane count."""
 
-    def __init__(self, problems, *, pdl=False, accumulate=False, atomic_f32=False, swiglu_f32=False, exchange=None):
+    def __init__(self, problems, *, pdl=False, accumulate=False, atomic_fixed=False, swiglu_fixed=False, exchange=None):
         self._lib = _lib.load()
-        self._arr, self._keep = marshal_problems(problems, atomic_f32=atomic_f32, swiglu_f32=swiglu_f32)
+        self._arr, self._keep = marshal_problems(problems, atomic_fixed=atomic_fixed, swiglu_fixed=swiglu_fixed)
         self._device = problems[0]["output"].device
         if self._device.index is None:
             self._device = torch.device("cuda", torch.cuda.current_device())
         self._flags = ((_lib.SAL_PDL if pdl else 0) | (_lib.SAL_ACCUMULATE if accumulate else 0)
-                       | (_lib.SAL_OUT_F32_ATOMIC if atomic_f32 else 0) | (_lib.SAL_SWIGLU_F32 if swiglu_f32 else 0))
+                       | (_lib.SAL_OUT_FIXED_ATOMIC if atomic_fixed else 0) | (_lib.SAL_SWIGLU_FIXED if swiglu_fixed else 0))
         self._exchange = exchange          # a ctypes SalExchange (and what it points to), or None
         handle = _lib._vp()
         with torch.cuda.device(self._device):
@@ -244,16 +246,17 @@ def prepare_grouped(problems, **kwargs) -> GroupedLaunch:
     return GroupedLaunch(problems, **kwargs)
 
 
-def lutgemv_grouped(problems, *, pdl=False, accumulate=False, atomic_f32=False, swiglu_f32=False):
+def lutgemv_grouped(problems, *, pdl=False, accumulate=False, atomic_fixed=False, swiglu_fixed=False):
     """Several independent mode-A products in one launch.  ``problems`` is a list
     of dicts with keys output, bWeight, alpha, bias (or None), d_input,
     mSize, kSize, nb, num_groups and optionally d_input_mul (the activation is then
     silu(d_input) * d_input_mul, computed while the tables are built).
 
-    ``atomic_f32=True``: every ``output`` is a float32 accumulator the product is ADDED to with fp32
-    atomics (no split-K reduction tail; summation order not fixed).  ``swiglu_f32=True``: d_input and
-    d_input_mul are such float32 accumulators."""
-    GroupedLaunch(problems, pdl=pdl, accumulate=accumulate, atomic_f32=atomic_f32, swiglu_f32=swiglu_f32)()
+    ``atomic_fixed=True``: every ``output`` is an int64 fixed-point accumulator (units of 2**-32, see
+    :data:`FIXED_ONE`) the product is ADDED to with integer atomics: no split-K reduction tail, and — integer
+    sums being independent of the order of arrival — still bit-identical from run to run.
+    ``swiglu_fixed=True``: d_input and d_input_mul are such accumulators."""
+    GroupedLaunch(problems, pdl=pdl, accumulate=accumulate, atomic_fixed=atomic_fixed, swiglu_fixed=swiglu_fixed)()
 
 
 def compiled_module():

@@ -13,6 +13,12 @@ from shiftaddllm_b200.decoder import SHAPES, BcqLlamaDecoder, benchmark
 pytestmark = pytest.mark.gpu
 
 
+def fixed(t):
+    """float tensor -> int64 fixed-point accumulator (units of 2**-32), the output format of SAL_OUT_FIXED_ATOMIC products."""
+    return torch.round(t.double() * float(2 ** 32)).to(torch.int64)
+
+
+
 def dense(lin):
     w = o.dequant_mode_a(lin.binaryWeight.cpu().numpy(), lin.alpha.cpu().numpy())
     return torch.from_numpy(w).cuda()            # [N, K] fp32
@@ -140,7 +146,7 @@ def test_split_attention_matches_torch(heads, kvh, hd, max_len, pos_v):
                                                             (64, 8, 128, 300, 0, True), (8, 8, 32, 64, 63, False)])
 def test_rope_attention_fused_equals_two_kernels(heads, kvh, hd, max_len, pos_v, f32):
     """Rotary step + cache write + attention in one kernel against the two separate helpers:
-    same cache contents and the same output; fp32 accumulator inputs are consumed and cleared."""
+    same cache contents and the same output; fixed-point accumulator inputs are consumed and cleared."""
     from shiftaddllm_b200 import decode_ops
 
     g = torch.Generator(device="cuda").manual_seed(pos_v + heads)
@@ -161,7 +167,7 @@ def test_rope_attention_fused_equals_two_kernels(heads, kvh, hd, max_len, pos_v,
     decode_ops.rope_kv_write(q_ref, k.half(), v.half(), cos, sin, pos, kc_ref, vc_ref, heads, kvh, hd)
     decode_ops.attention_decode(q_ref, kc_ref, vc_ref, pos, out_ref, heads, kvh, hd, scale, ws)
     # one kernel
-    qi, ki, vi = (q.clone(), k.clone(), v.clone()) if f32 else (q.half(), k.half(), v.half())
+    qi, ki, vi = (fixed(q), fixed(k), fixed(v)) if f32 else (q.half(), k.half(), v.half())
     out = torch.empty_like(out_ref)
     assert decode_ops.rope_attention_decode(qi, ki, vi, cos, sin, pos, kc, vc, out, heads, kvh, hd, scale, ws)
     torch.cuda.synchronize()
@@ -187,31 +193,32 @@ def test_rmsnorm_helpers_all_sizes(n):
     out, xo = torch.empty_like(x), torch.empty_like(x)
     decode_ops.residual_rmsnorm(x, d, w, out, xo, 1e-5)
     assert torch.equal(xo, t) and float((out.float() - ref).abs().max()) < 6e-3
-    d32, za = d.float(), torch.ones(40000, device="cuda")
+    d32, za = fixed(d), torch.ones(40000, dtype=torch.int64, device="cuda")
     out2, x_inplace = torch.empty_like(x), x.clone()
-    decode_ops.residual_rmsnorm_f32acc(x_inplace, d32, w, out2, x_inplace, 1e-5, za, None)
+    decode_ops.residual_rmsnorm_fixedacc(x_inplace, d32, w, out2, x_inplace, 1e-5, za, None)
     assert torch.equal(x_inplace, t) and torch.equal(out2, out)
     assert not d32.any() and not za.any()
 
 
 def test_accumulator_consuming_helpers():
-    """The fp32-accumulator variants give what the fp16 helpers give on the rounded accumulator, and
+    """The accumulator-consuming variants give what the fp16 helpers give on the rounded accumulator, and
     leave every accumulator they were handed at zero."""
     from shiftaddllm_b200 import decode_ops
 
     g = torch.Generator(device="cuda").manual_seed(3)
     n = 4096
     x = torch.randn(1, n, device="cuda", generator=g).half()
-    d32 = torch.randn(1, n, device="cuda", generator=g)
+    d_f = torch.randn(1, n, device="cuda", generator=g)
+    d32 = fixed(d_f)
     w = (1 + 0.1 * torch.randn(n, device="cuda", generator=g)).half()
-    za, zb = torch.ones(11008, device="cuda"), torch.ones(300, device="cuda")
+    za, zb = torch.ones(11008, dtype=torch.int64, device="cuda"), torch.ones(300, dtype=torch.int64, device="cuda")
     out, xo = torch.empty_like(x), torch.empty_like(x)
     out_ref, xo_ref = torch.empty_like(x), torch.empty_like(x)
-    decode_ops.residual_rmsnorm(x, d32.half(), w, out_ref, xo_ref, 1e-5)
-    decode_ops.residual_rmsnorm_f32acc(x, d32, w, out, xo, 1e-5, za, zb)
+    decode_ops.residual_rmsnorm(x, d_f.half(), w, out_ref, xo_ref, 1e-5)
+    decode_ops.residual_rmsnorm_fixedacc(x, d32, w, out, xo, 1e-5, za, zb)
     assert torch.equal(xo, xo_ref) and float((out.float() - out_ref.float()).abs().max()) < 2e-3
     assert not d32.any() and not za.any() and not zb.any()
-    decode_ops.residual_rmsnorm_f32acc(x, None, w, out, None, 1e-5)
+    decode_ops.residual_rmsnorm_fixedacc(x, None, w, out, None, 1e-5)
     decode_ops.residual_rmsnorm(x, None, w, out_ref, None, 1e-5)
     assert float((out.float() - out_ref.float()).abs().max()) < 2e-3
 
@@ -228,9 +235,10 @@ def test_accumulator_consuming_helpers():
     q_ref, k_ref, v_ref = q32.half(), k32.half(), v32.half()
     decode_ops.rope_kv_write(q_ref, k_ref, v_ref, cos, sin, pos, kc_ref, vc_ref, heads, kvh, hd)
     q_out = torch.empty(heads * hd, dtype=torch.float16, device="cuda")
-    decode_ops.rope_kv_write_f32acc(q32, k32, v32, q_out, cos, sin, pos, kc, vc, heads, kvh, hd)
+    qa, ka, va = fixed(q32), fixed(k32), fixed(v32)
+    decode_ops.rope_kv_write_fixedacc(qa, ka, va, q_out, cos, sin, pos, kc, vc, heads, kvh, hd)
     assert torch.equal(q_out, q_ref) and torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
-    assert not q32.any() and not k32.any() and not v32.any()
+    assert not qa.any() and not ka.any() and not va.any()
 
 
 @pytest.mark.parametrize("mode", ["torch", "fused", "atomic"])
@@ -288,8 +296,9 @@ def test_chunked_prefill_matches_token_by_token(chunk):
 
 
 def test_atomic_mode_tracks_the_deterministic_mode():
-    """fp32-atomic accumulation only changes the summation order: greedy tokens over a short
-    generation agree with the deterministic path, and the accumulators are left clean."""
+    """Fixed-point atomic accumulation only changes where the fp16 rounding happens: greedy tokens over a short
+    generation agree with the fp16-output path, the accumulators are left clean, and a second run gives
+    bit-identical logits (integer sums do not depend on the order in which thread blocks arrive)."""
     a = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=64, seed=4, fused=True)
     b = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=64, seed=4, fused=True, atomic=True)
     for m in (a, b):
@@ -298,12 +307,14 @@ def test_atomic_mode_tracks_the_deterministic_mode():
     ta, tb = a.generate(6).cpu(), b.generate(6).cpu()
     assert torch.equal(ta, tb)
     torch.cuda.synchronize()
-    for buf in (b._q32, b._k32, b._v32, b._o32, b._gate32, b._up32):
+    for buf in (b._qacc, b._kacc, b._vacc, b._oacc, b._gateacc, b._upacc):
         assert float(buf.abs().max()) == 0.0          # consumed and cleared (down32 is cleared by the next step)
+    first_logits = b.logits.clone()
     b.capture()
     b.reset()
     b.feed([3, 1, 4, 1, 5])
     assert torch.equal(b.generate(6).cpu(), ta)
+    assert torch.equal(b.logits, first_logits)
 
 
 def test_batch_decoder_matches_single_sequences():

@@ -197,46 +197,58 @@ def test_fused_swiglu_input():
         assert o.max_rel_err(y_fused.float().cpu().numpy(), ref) <= TOL
 
 
+FIXED_ONE = float(2 ** 32)   # a fixed-point accumulator counts units of 2**-32
+
+
 @pytest.mark.parametrize("k,n", [(768, 768), (4096, 4096), (11008, 4096)])
-def test_fp32_atomic_output(k, n):
-    """Opt-in fp32 output accumulated with atomics (every split adds its partial; bias added once):
-    tighter than the fp16 output because nothing is rounded to fp16, and it accumulates onto what
-    the buffer held."""
+def test_fixed_point_atomic_output(k, n):
+    """Opt-in accumulator output (int64, units of 2**-32) that every K split adds its partial sum to with integer
+    atomics (bias added once): tighter than the fp16 output because nothing is rounded to fp16, it accumulates
+    onto what the buffer held, and — integer sums not depending on the order of arrival — it is bit-identical
+    from call to call."""
     layer = synth.make_layer(k, n, 3, 128, packed_draw=True, bias=True, layer_index=5)
     ref = ref_mode_a(layer)
     base = torch.randn(1, n, generator=torch.Generator().manual_seed(2)).cuda()
-    y = base.clone()
-    prob = dict(output=y, bWeight=dev(layer.bWeight), alpha=dev(layer.alpha), bias=dev(layer.bias),
-                d_input=dev(layer.x), mSize=n, kSize=k, nb=3, num_groups=k // 128)
-    lutgemm.lutgemv_grouped([prob], atomic_f32=True)
-    torch.cuda.synchronize()
-    assert o.max_rel_err((y - base).cpu().numpy(), ref) <= 1e-4
+    base_fixed = torch.round(base.double() * FIXED_ONE).to(torch.int64)
+    prob = dict(bWeight=dev(layer.bWeight), alpha=dev(layer.alpha), bias=dev(layer.bias), d_input=dev(layer.x), mSize=n, kSize=k,
+                nb=3, num_groups=k // 128)
+    results = []
+    for _ in range(3):
+        y = base_fixed.clone()
+        lutgemm.lutgemv_grouped([dict(output=y, **prob)], atomic_fixed=True)
+        torch.cuda.synchronize()
+        results.append(y)
+    got = ((results[0] - base_fixed).double() / FIXED_ONE).cpu().numpy()
+    assert o.max_rel_err(got, ref) <= 1e-4
+    assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])      # deterministic
     assert_status_clean()
     # refused where the fixed-order reduction is the only implementation: M > 1
     lib = _lib.load()
     x2 = torch.zeros(2, k, dtype=torch.float16, device="cuda")
-    y2 = torch.zeros(2, n, device="cuda")
+    y2 = torch.zeros(2, n, dtype=torch.int64, device="cuda")
     rc = lib.sal_lutgemv_shift_scale(prob["bWeight"].data_ptr(), prob["alpha"].data_ptr(), None, x2.data_ptr(),
-                                     y2.data_ptr(), 2, k, n, 3, k // 128, _lib.SAL_OUT_F32_ATOMIC, None, 0,
+                                     y2.data_ptr(), 2, k, n, 3, k // 128, _lib.SAL_OUT_FIXED_ATOMIC, None, 0,
                                      torch.cuda.current_stream().cuda_stream)
     assert rc == _lib.SAL_E_UNSUPPORTED
 
 
-def test_fp32_atomic_swiglu_input():
-    """down projection reading fp32 gate/up accumulators and adding into an fp32 output."""
+def test_fixed_point_swiglu_input():
+    """down projection reading fixed-point gate/up accumulators and adding into a fixed-point output."""
     import torch.nn.functional as F
 
     layer = synth.make_layer(2048, 512, 3, 128, packed_draw=True)
     g = torch.Generator().manual_seed(11)
     gate, up = torch.randn(1, 2048, generator=g).cuda(), torch.randn(1, 2048, generator=g).cuda()
-    y = torch.zeros(1, 512, device="cuda")
-    lutgemm.lutgemv_grouped([dict(output=y, bWeight=dev(layer.bWeight), alpha=dev(layer.alpha), bias=None, d_input=gate,
-                                  d_input_mul=up, mSize=512, kSize=2048, nb=3, num_groups=16)],
-                            atomic_f32=True, swiglu_f32=True)
+    gate_fixed = torch.round(gate.double() * FIXED_ONE).to(torch.int64)
+    up_fixed = torch.round(up.double() * FIXED_ONE).to(torch.int64)
+    y = torch.zeros(1, 512, dtype=torch.int64, device="cuda")
+    lutgemm.lutgemv_grouped([dict(output=y, bWeight=dev(layer.bWeight), alpha=dev(layer.alpha), bias=None, d_input=gate_fixed,
+                                  d_input_mul=up_fixed, mSize=512, kSize=2048, nb=3, num_groups=16)],
+                            atomic_fixed=True, swiglu_fixed=True)
     torch.cuda.synchronize()
     w = o.dequant_mode_a(layer.bWeight.numpy(), layer.alpha.numpy())
-    act = (F.silu(gate) * up).half().float()          # the table build rounds the activation to fp16
-    assert o.max_rel_err(y.cpu().numpy(), o.linear_fp32(act.cpu().numpy(), w)) <= 2e-3
+    act = (F.silu(gate.half().float()).half().float() * up.half().float()).half().float()   # rounded to fp16 at every step, as the table build does
+    assert o.max_rel_err((y.double() / FIXED_ONE).cpu().numpy(), o.linear_fp32(act.cpu().numpy(), w)) <= 2e-3
 
 
 def test_hand_checkable():
