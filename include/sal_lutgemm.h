@@ -206,7 +206,11 @@ int sal_lutgemv_grouped(const sal_problem *problems, int count, unsigned flags,
  * counter reaches world * writers — sal_exchange_wait does that wait.
  * peer_buffers / peer_flags: device pointers valid on this GPU for every rank's buffer (fp16) and
  * flag array (uint32), e.g. from CUDA IPC or torch symmetric memory; flags start at zero.
- * Use at least two slots in rotation (a slot is cleared by the wait that consumed it).  M = 1 only.
+ * Use at least two slots in rotation (a slot is cleared by the wait that consumed it), and never make one
+ * region of the gather buffers the target of two launches in a row: a peer that is one launch ahead may already
+ * be storing launch L + 1's outputs into this rank's buffer while this rank still reads launch L's (it cannot be
+ * further ahead: its launch L + 2 waits for this rank's arrival of L + 1, issued after this rank's reads of L).
+ * The arrival is published by one release-add per peer after a CTA barrier.  M = 1 only.
  */
 typedef struct sal_exchange {
     int world, rank, slot;
@@ -238,6 +242,10 @@ int sal_prepare_grouped(const sal_problem *problems, int count, unsigned flags, 
 size_t sal_prepared_workspace_bytes(const sal_prepared *prepared);
 int sal_prepared_writers(const sal_prepared *prepared);
 int sal_launch_prepared(const sal_prepared *prepared, void *workspace, size_t workspace_bytes, int slot, void *stream);
+/* `count` prepared launches enqueued one after the other by ONE call (a decoder block, a whole token): the host
+ * cost per launch is then the CUDA launch itself.  `slots` (may be NULL) gives the counter slot of each launch. */
+int sal_launch_prepared_sequence(const sal_prepared *const *prepared, int count, const int *slots, void *workspace,
+                                 size_t workspace_bytes, void *stream);
 void sal_destroy_prepared(sal_prepared *prepared);
 
 /* Enqueues a one-thread kernel that waits (bounded, about one second; SAL_E_TIMEOUT is recorded

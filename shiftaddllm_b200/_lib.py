@@ -62,6 +62,7 @@ SIGNATURES = {
     "sal_prepared_workspace_bytes": (_sz, [_vp]),
     "sal_prepared_writers": (_i, [_vp]),
     "sal_launch_prepared": (_i, [_vp, _vp, _sz, _i, _vp]),
+    "sal_launch_prepared_sequence": (_i, [ctypes.POINTER(_vp), _i, ctypes.POINTER(_i), _vp, _sz, _vp]),
     "sal_destroy_prepared": (None, [_vp]),
     "sal_plan_shift_scale": (_i, [_i, _i, _i, _i, _i, ctypes.POINTER(SalPlanInfo)]),
     # include/sal_decode_ops.h

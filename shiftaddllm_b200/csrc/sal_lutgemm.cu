@@ -664,6 +664,13 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         if constexpr (BLK) consumer_barrier(NCW * 32);  // one set of tables: the previous K block must be finished by all
         if (!SAL_ABLATED(P, 2)) build_block(kb, PAR, warp, std::integral_constant<int, NCW>{});
         consumer_barrier(NCW * 32);
+        // The activations of the next K block are asked into L1 now, so that its table build does not start with
+        // a trip to L2 (no registers held meanwhile; one 16-byte line piece per lane of one warp covers the block).
+        if (SWIGLU == 0 && warp == 0 && kb + 1 < kb_end && !SAL_ABLATED(P, 128)) {
+            const __half *nx0 = xrow0 + (size_t)(kb + 1) * KB_FEATS + 8 * lane;
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(nx0));
+            if (ROWS == 2) asm volatile("prefetch.global.L1 [%0];" ::"l"(xrow1 + (size_t)(kb + 1) * KB_FEATS + 8 * lane));
+        }
         // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
         // unrolling it over the column tiles overflows the instruction cache.  acc[] is then
         // indexed dynamically and lives in (L1-resident) local memory: two accesses per tile.
@@ -2004,6 +2011,16 @@ int sal_launch_prepared(const sal_prepared *prepared, void *workspace, size_t wo
     if (!cuda_ok(cudaGetDevice(&dev)) || dev != prepared->device) return SAL_E_DEVICE;
     for (int c = 0; c < prepared->nlaunch; ++c) {
         const int rc = launch_built(prepared->launch[c], workspace, workspace_bytes, slot, reinterpret_cast<cudaStream_t>(stream));
+        if (rc != SAL_OK) return rc;
+    }
+    return SAL_OK;
+}
+
+int sal_launch_prepared_sequence(const sal_prepared *const *prepared, int count, const int *slots, void *workspace,
+                                 size_t workspace_bytes, void *stream) {
+    if (!prepared || count < 0) return SAL_E_NULL;
+    for (int i = 0; i < count; ++i) {
+        const int rc = sal_launch_prepared(prepared[i], workspace, workspace_bytes, slots ? slots[i] : -1, stream);
         if (rc != SAL_OK) return rc;
     }
     return SAL_OK;

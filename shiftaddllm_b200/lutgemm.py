@@ -240,6 +240,35 @@ class GroupedLaunch:
             self._lib.sal_destroy_prepared(handle)
 
 
+class LaunchSequence:
+    """Several prepared launches enqueued by one call into the library (`sal_launch_prepared_sequence`): what a
+    decoder block or a whole token is.  All launches must belong to one device."""
+
+    def __init__(self, launches):
+        self._launches = list(launches)
+        if not self._launches:
+            raise RuntimeError("an empty launch sequence")
+        self._lib = _lib.load()
+        self._device = self._launches[0]._device
+        if any(l._device != self._device for l in self._launches):
+            raise RuntimeError("all launches of a sequence must be on one device")
+        self._handles = (_lib._vp * len(self._launches))(*[l._handle for l in self._launches])
+        self._need = max(l._need for l in self._launches)
+
+    def __call__(self):
+        dev = self._device
+        if torch.cuda.current_device() != dev.index:
+            with torch.cuda.device(dev):
+                return self()
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        ws = _workspaces.get((dev.index, stream))
+        if ws is None or ws.numel() < self._need:
+            ws = workspace_bytes(dev, self._need)
+        rc = self._lib.sal_launch_prepared_sequence(self._handles, len(self._launches), None, ws.data_ptr(), ws.numel(), stream)
+        if rc != 0:
+            _lib.check(rc, "sal_launch_prepared_sequence")
+
+
 def prepare_grouped(problems, **kwargs) -> GroupedLaunch:
     """``lutgemv_grouped`` split in two: the checks and the marshalling happen here, once; the returned
     object is called every time the launch is wanted (a few microseconds of host time per call)."""
