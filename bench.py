@@ -537,7 +537,7 @@ def run_ours(args, rank, world, device):
             stream.wait_event(ev_x_in[i])
             lset.x_all.copy_(x_stage, non_blocking=True)
             ev_x_used[i].record(stream)
-            head.step()
+            replay()
             if i > 0:
                 stream.wait_event(ev_y_done[i - 1])
             y_stage.copy_(y_src, non_blocking=True)
@@ -564,8 +564,8 @@ def run_ours(args, rank, world, device):
         e2e_s = float(t.item())
         out["e2e"] = {"value": round(total / e2e_s / 1e9, 1), "unit": "GB/s", "ms_per_step": round(e2e_s * 1e3, 3),
                       "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
-                      "api": ("shiftaddllm_b200.lutgemm.prepare_grouped launches (prepared once), enqueued eagerly from Python through "
-                              "lutgemm.LaunchSequence (no graph); every step copies its activations in from pinned host memory and its results out "
+                      "api": ("shiftaddllm_b200.lutgemm.prepare_grouped launches (prepared once, enqueued through lutgemm.LaunchSequence), "
+                              + ("the step's launches replayed as a CUDA graph" if graphed else "enqueued eagerly") + "; every step copies its activations in from pinned host memory and its results out "
                               "to pinned host memory, the PCIe copies on a second stream overlapping the neighbouring steps")}
         del x_stage, y_stage
     out["device_status"] = device_status(lib, device, stream)
@@ -774,19 +774,28 @@ def shapes_record(args, timer, device):
                        for _ in range(copies)]
                 x = torch.randn(m, k, device=device, generator=gen).half()
                 y = torch.empty(m, n, dtype=torch.float16, device=device)
-                alpha = torch.exp2(-torch.randint(2, 9, (k // G, q, n), device=device, generator=gen).float()).half()
-                launches = [lutgemm.prepare_grouped([dict(output=y, bWeight=bw, alpha=alpha, bias=None, d_input=x, mSize=n, kSize=k,
-                                                          nb=q, num_groups=k // G)], pdl=True) for bw in bws]
+                if args.mode == "block_int8":     # the layout of the "Lat." checkpoints: LutLinear.forward's call
+                    alpha = torch.randint(-8, -1, (k // 8, q, n // BLOCK_GS, 3), device=device, generator=gen).to(torch.int8)
+                    alpha[:, :, :, 2] = -128
+                    launches = None
 
-                def step():
-                    for launch in launches:
-                        launch()
+                    def step():
+                        for bw in bws:
+                            lutgemm.lutgemm_block_fused(y, bw, alpha, None, x, n, k, q, n // BLOCK_GS, pdl=True)
+                else:
+                    alpha = torch.exp2(-torch.randint(2, 9, (k // G, q, n), device=device, generator=gen).float()).half()
+                    launches = [lutgemm.prepare_grouped([dict(output=y, bWeight=bw, alpha=alpha, bias=None, d_input=x, mSize=n, kSize=k,
+                                                              nb=q, num_groups=k // G)], pdl=True) for bw in bws]
+
+                    def step():
+                        for launch in launches:
+                            launch()
 
                 replay, _ = timer.capture(step)
                 ms, _ = timer.timed(replay, 10)
                 us = ms * 1e3 / copies
-                nbytes = algorithmic_bytes(k, n, q, m=m)
-                rows.append({"K": k, "N": n, "q": q, "M": m, "us_per_call": round(us, 3), "gbps": round(nbytes / us / 1e3, 1),
+                nbytes = algorithmic_bytes(k, n, q, m=m, alpha_bytes=3 if args.mode == "block_int8" else 2)
+                rows.append({"K": k, "N": n, "q": q, "M": m, "mode": args.mode, "us_per_call": round(us, 3), "gbps": round(nbytes / us / 1e3, 1),
                              "frac_of_measured_hbm": round(nbytes / us / 1e3 / peak, 4)})
                 del launches, bws, replay
     return rows
@@ -953,6 +962,8 @@ def main():
                          "process for profiler captures, the launches are the same")
     ap.add_argument("--shapes", default="4096x4096,4096x11008,11008x4096", help="--legs shapes: KxN list")
     ap.add_argument("--wbits", default="3", help="--legs shapes: plane counts")
+    ap.add_argument("--mode", default="row", choices=["row", "block_int8"],
+                    help="--legs shapes: alpha per K group and column (row), or int8 multipliers per 8 inputs x 16 outputs (block_int8)")
     ap.add_argument("--batch", default="1", help="--legs shapes: activation rows")
     args = ap.parse_args()
     args.legs = [] if args.legs == "none" else [leg for leg in args.legs.split(",") if leg]

@@ -174,8 +174,7 @@ def test_prepared_launch_through_the_c_abi():
     assert lib.sal_launch_prepared(handle, ws.data_ptr(), 1024, -1, stream) == _lib.SAL_E_WORKSPACE
     # several prepared launches enqueued by one call
     second = ctypes.c_void_p()
-    arr2, keep2 = lutgemm.marshal_problems([lset.problem(p) for p in flat[:3]])
-    assert lib.sal_prepare_grouped(arr2, 3, _lib.SAL_PDL, None, ctypes.byref(second)) == 0
+    assert lib.sal_prepare_grouped(arr, len(flat), _lib.SAL_PDL, None, ctypes.byref(second)) == 0      # same problems: same plan
     handles = (ctypes.c_void_p * 2)(handle, second)
     lset.y_all.zero_()
     assert lib.sal_launch_prepared_sequence(handles, 2, None, ws.data_ptr(), ws.numel(), stream) == 0
