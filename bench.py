@@ -514,14 +514,14 @@ def run_ours(args, rank, world, device):
 
     # ---- end to end: host activations in, host results out, through the public Python API
     if "e2e" in legs:
-        # Host buffers in, host buffers out, every step.  The PCIe copies run on a second stream into / out of
+        # Host buffers in, host buffers out, every step.  The PCIe copies run on two further streams into / out of
         # device staging buffers, so that they overlap the neighbouring steps' kernels; the compute stream only
         # does two device-to-device copies per step (activations in, results out).
         x_host = lset.x_all.cpu().pin_memory()
         y_src = (peer.buffer if fused else y_full) if world > 1 else lset.y_all
         y_host = torch.empty(y_src.shape, dtype=torch.float16).pin_memory()
         x_stage, y_stage = torch.empty_like(lset.x_all), torch.empty_like(y_src)
-        copy_stream = torch.cuda.Stream(device)
+        in_stream, out_stream = torch.cuda.Stream(device), torch.cuda.Stream(device)   # one PCIe direction each
         e2e_steps = max(3, min(args.steps, 10))
         ev_x_in = [torch.cuda.Event() for _ in range(e2e_steps + 2)]      # activations of step i are on the device
         ev_x_used = [torch.cuda.Event() for _ in range(e2e_steps + 2)]    # step i has taken them out of the staging buffer
@@ -529,11 +529,11 @@ def run_ours(args, rank, world, device):
         ev_y_done = [torch.cuda.Event() for _ in range(e2e_steps + 2)]    # ... and have left for the host
 
         def e2e_step(i):
-            with torch.cuda.stream(copy_stream):
+            with torch.cuda.stream(in_stream):
                 if i > 0:
-                    copy_stream.wait_event(ev_x_used[i - 1])
+                    in_stream.wait_event(ev_x_used[i - 1])
                 x_stage.copy_(x_host, non_blocking=True)
-                ev_x_in[i].record(copy_stream)
+                ev_x_in[i].record(in_stream)
             stream.wait_event(ev_x_in[i])
             lset.x_all.copy_(x_stage, non_blocking=True)
             ev_x_used[i].record(stream)
@@ -542,10 +542,10 @@ def run_ours(args, rank, world, device):
                 stream.wait_event(ev_y_done[i - 1])
             y_stage.copy_(y_src, non_blocking=True)
             ev_y_out[i].record(stream)
-            with torch.cuda.stream(copy_stream):
-                copy_stream.wait_event(ev_y_out[i])
+            with torch.cuda.stream(out_stream):
+                out_stream.wait_event(ev_y_out[i])
                 y_host.copy_(y_stage, non_blocking=True)
-                ev_y_done[i].record(copy_stream)
+                ev_y_done[i].record(out_stream)
 
         with torch.cuda.stream(stream):
             e2e_step(0)
@@ -566,7 +566,7 @@ def run_ours(args, rank, world, device):
                       "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": y_host.numel() * 2,
                       "api": ("shiftaddllm_b200.lutgemm.prepare_grouped launches (prepared once, enqueued through lutgemm.LaunchSequence), "
                               + ("the step's launches replayed as a CUDA graph" if graphed else "enqueued eagerly") + "; every step copies its activations in from pinned host memory and its results out "
-                              "to pinned host memory, the PCIe copies on a second stream overlapping the neighbouring steps")}
+                              "to pinned host memory, the PCIe copies on two further streams (one per direction) overlapping the neighbouring steps")}
         del x_stage, y_stage
     out["device_status"] = device_status(lib, device, stream)
 

@@ -70,6 +70,19 @@ int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_fixe
                               const int64_t *pos, void *k_cache, void *v_cache, void *out, int heads, int kv_heads, int hd,
                               int max_len, float scale, void *workspace, size_t workspace_bytes, void *stream);
 
+/* The two helpers above for `batch` sequences decoded in lock step (one shared position *pos; 1 <= batch <= 64), so
+ * that a lock-step batch decoder has no framework operator between its small-batch LUT products either.
+ * sal_residual_rmsnorm_rows_f16: `rows` rows of n elements (x, delta, out, x_out are [rows][n]; one weight vector).
+ * sal_rope_attention_decode_batch: q [batch][heads][hd], k_new / v_new [batch][kv_heads][hd] (fp16, un-rotated),
+ * caches [batch][max_len][kv_heads][hd], out [batch][heads][hd]; scratch of batch x
+ * sal_attention_workspace_bytes(heads, hd) bytes, zero-filled once.  Per sequence exactly what
+ * sal_rope_attention_decode computes. */
+int sal_residual_rmsnorm_rows_f16(const void *x, const void *delta, const void *weight, void *out, void *x_out, int rows, int n,
+                                  float eps, void *stream);
+int sal_rope_attention_decode_batch(void *q, void *k_new, void *v_new, const void *cos, const void *sin, const int64_t *pos,
+                                    void *k_cache, void *v_cache, void *out, int batch, int heads, int kv_heads, int hd, int max_len,
+                                    float scale, void *workspace, size_t workspace_bytes, void *stream);
+
 /* out = silu(gate) * up, fp16 vectors of n elements. */
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream);
 

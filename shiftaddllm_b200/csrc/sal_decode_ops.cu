@@ -69,6 +69,13 @@ __global__ void __launch_bounds__(1024) residual_rmsnorm_kernel(const __half *x,
     __shared__ float red[32];
     extern __shared__ float tbuf[];  // n floats
     pdl_prologue();
+    {   // one CTA per row (grid.x rows of n elements each; the weight is shared)
+        const size_t row = (size_t)blockIdx.x * n;
+        x += row;
+        out += row;
+        if (delta) delta += row;
+        if (x_out) x_out += row;
+    }
     if (fast_rows_ok(n, x, delta, w, out, x_out)) {
         // n <= 8 x threads, everything 16-byte aligned: a thread keeps its 8 elements in registers, every
         // operand is fetched with one 16-byte load and all loads are in flight together
@@ -390,6 +397,11 @@ struct RopeArgs {
     void *k_new, *v_new;       // [kv_heads][hd], fp16 (ROPE 1) or fixed-point accumulators (ROPE 2)
     const float *cos_t, *sin_t;  // [max_len][hd / 2]
 };
+// Sequences decoded in lock step (one shared position): sequence blockIdx.z finds its operands these many BYTES
+// further on.  All zero for a single sequence.
+struct SeqStrides {
+    size_t q, kv_new, cache, out, scratch;
+};
 template <int ROPE>
 __device__ __forceinline__ float rope_in(const void *p, size_t i) {
     if (ROPE == 2) return __half2float(__float2half_rn(acc_value(reinterpret_cast<const acc_t *>(p)[i])));
@@ -401,8 +413,19 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
                                                                           const int64_t *pos_p, __half *out, float *partial,
                                                                           unsigned *counters, int kv_heads, int hd,
                                                                           int max_len, float scale, int nsplit,
-                                                                          int slice_cap, RopeArgs ra) {
+                                                                          int slice_cap, RopeArgs ra, SeqStrides ss) {
     extern __shared__ __align__(16) float smem_f[];
+    {
+        const size_t z = blockIdx.z;
+        q = reinterpret_cast<const char *>(q) + z * ss.q;
+        ra.k_new = reinterpret_cast<char *>(ra.k_new) + z * ss.kv_new;
+        ra.v_new = reinterpret_cast<char *>(ra.v_new) + z * ss.kv_new;
+        k_cache = reinterpret_cast<__half *>(reinterpret_cast<char *>(k_cache) + z * ss.cache);
+        v_cache = reinterpret_cast<__half *>(reinterpret_cast<char *>(v_cache) + z * ss.cache);
+        out = reinterpret_cast<__half *>(reinterpret_cast<char *>(out) + z * ss.out);
+        partial = reinterpret_cast<float *>(reinterpret_cast<char *>(partial) + z * ss.scratch);
+        counters = reinterpret_cast<unsigned *>(reinterpret_cast<char *>(counters) + z * ss.scratch);
+    }
     __shared__ float s_m[G], s_l[G];
     __shared__ float s_w[ATTN_MAX_SPLIT][G];
     __shared__ int s_is_last;
@@ -656,7 +679,7 @@ constexpr size_t ATTN_WS_HEADER = 1024;   // arrival counters, one per kv head (
 template <int G, bool STAGE_V, int ROPE>
 int launch_attention_variant(size_t smem, const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
                              int kv_heads, int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap,
-                             const RopeArgs &ra, cudaStream_t stream) {
+                             const RopeArgs &ra, cudaStream_t stream, int batch = 1, const SeqStrides &ss = SeqStrides{}) {
     if (smem + 2048 > 48 * 1024) {   // the kernel's static shared memory counts against the default limit too
         // the attribute belongs to the (function, device) pair: remember it per device ordinal
         static size_t configured[64];
@@ -669,39 +692,41 @@ int launch_attention_variant(size_t smem, const void *q, const void *k_cache, co
             configured[dev] = smem;
         }
     }
-    return launch_pdl(attention_split_kernel<G, STAGE_V, ROPE>, dim3(kv_heads, nsplit), dim3(ATTN_WARPS * 32), smem, stream, q,
+    return launch_pdl(attention_split_kernel<G, STAGE_V, ROPE>, dim3(kv_heads, nsplit, batch), dim3(ATTN_WARPS * 32), smem, stream, q,
                       reinterpret_cast<__half *>(const_cast<void *>(k_cache)), reinterpret_cast<__half *>(const_cast<void *>(v_cache)),
                       pos, reinterpret_cast<__half *>(out),
                       reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + ATTN_WS_HEADER),
-                      reinterpret_cast<unsigned *>(workspace), kv_heads, hd, max_len, scale, nsplit, slice_cap, ra);
+                      reinterpret_cast<unsigned *>(workspace), kv_heads, hd, max_len, scale, nsplit, slice_cap, ra, ss);
 }
 
 template <int G, int ROPE>
 int launch_attention_split(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int kv_heads,
                            int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap, const RopeArgs &ra,
-                           cudaStream_t stream) {
+                           cudaStream_t stream, int batch = 1, const SeqStrides &ss = SeqStrides{}) {
     const size_t base = (size_t)(G * hd + G * slice_cap + ATTN_WARPS * G * hd) * sizeof(float);
     const size_t staged = base + (size_t)slice_cap * hd * sizeof(__half);
     if (staged <= 96 * 1024)
         return launch_attention_variant<G, true, ROPE>(staged, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale,
-                                                       workspace, nsplit, slice_cap, ra, stream);
+                                                       workspace, nsplit, slice_cap, ra, stream, batch, ss);
     if (base > 200 * 1024) return SAL_E_UNSUPPORTED;
     return launch_attention_variant<G, false, ROPE>(base, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace,
-                                                    nsplit, slice_cap, ra, stream);
+                                                    nsplit, slice_cap, ra, stream, batch, ss);
 }
 
 template <int ROPE>
 int attention_split_entry(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int heads,
                           int kv_heads, int hd, int max_len, float scale, void *workspace, size_t workspace_bytes,
-                          const RopeArgs &ra, void *stream) {
+                          const RopeArgs &ra, void *stream, int batch = 1) {
     if (!q || !k_cache || !v_cache || !pos || !out || !workspace) return SAL_E_NULL;
+    if (batch < 1 || batch > 64) return SAL_E_SHAPE;
     if (heads < 1 || kv_heads < 1 || kv_heads > 256 || heads % kv_heads || max_len < 1 || max_len > 65536) return SAL_E_SHAPE;
     if (hd != 32 && hd != 64 && hd != 128 && hd != 256) return SAL_E_UNSUPPORTED;
-    if (workspace_bytes < ATTN_WS_HEADER + (size_t)heads * ATTN_MAX_SPLIT * (size_t)(hd + 2) * sizeof(float)) return SAL_E_WORKSPACE;
+    const size_t ws_seq = ATTN_WS_HEADER + (size_t)heads * ATTN_MAX_SPLIT * (size_t)(hd + 2) * sizeof(float);   // per sequence
+    if (workspace_bytes < ws_seq * (size_t)batch) return SAL_E_WORKSPACE;
     if ((reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) return SAL_E_ALIGN;
     const int G = heads / kv_heads;
     // about three CTAs per SM (they are small), at least ~16 positions per slice at the longest context
-    int nsplit = (444 + kv_heads - 1) / kv_heads;
+    int nsplit = (444 + kv_heads * batch - 1) / (kv_heads * batch);
     if (nsplit > ATTN_MAX_SPLIT) nsplit = ATTN_MAX_SPLIT;
     if (G >= 8 && nsplit > ATTN_MAX_SPLIT / 2) nsplit = ATTN_MAX_SPLIT / 2;   // the merge grows with G x slices (measured)
     if (nsplit > (max_len + 15) / 16) nsplit = (max_len + 15) / 16;
@@ -710,11 +735,21 @@ int attention_split_entry(const void *q, const void *k_cache, const void *v_cach
     // shared memory are written with 16-byte stores
     const int slice_cap = ((max_len + nsplit - 1) / nsplit + 3) & ~3;
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+    // sequences in lock step: operands of sequence z lie z rows / caches / scratch blocks further on
+    const size_t qelem = ROPE == 2 ? sizeof(acc_t) : sizeof(__half);
+    SeqStrides ss = {};
+    if (batch > 1) {
+        ss.q = (size_t)heads * hd * qelem;
+        ss.kv_new = (size_t)kv_heads * hd * qelem;
+        ss.cache = (size_t)max_len * kv_heads * hd * sizeof(__half);
+        ss.out = (size_t)heads * hd * sizeof(__half);
+        ss.scratch = ws_seq;
+    }
     switch (G) {
-        case 1: return launch_attention_split<1, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
-        case 2: return launch_attention_split<2, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
-        case 4: return launch_attention_split<4, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
-        case 8: return launch_attention_split<8, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s);
+        case 1: return launch_attention_split<1, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
+        case 2: return launch_attention_split<2, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
+        case 4: return launch_attention_split<4, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
+        case 8: return launch_attention_split<8, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
         default: return SAL_E_UNSUPPORTED;
     }
 }
@@ -813,6 +848,25 @@ int sal_rope_attention_decode(void *q, void *k_new, void *v_new, int inputs_fixe
                                                  workspace_bytes, ra, stream)
                       : attention_split_entry<1>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace,
                                                  workspace_bytes, ra, stream);
+}
+
+int sal_rope_attention_decode_batch(void *q, void *k_new, void *v_new, const void *cos, const void *sin, const int64_t *pos,
+                                    void *k_cache, void *v_cache, void *out, int batch, int heads, int kv_heads, int hd, int max_len,
+                                    float scale, void *workspace, size_t workspace_bytes, void *stream) {
+    if (!k_new || !v_new || !cos || !sin) return SAL_E_NULL;
+    const RopeArgs ra = {k_new, v_new, reinterpret_cast<const float *>(cos), reinterpret_cast<const float *>(sin)};
+    return attention_split_entry<1>(q, k_cache, v_cache, pos, out, heads, kv_heads, hd, max_len, scale, workspace, workspace_bytes, ra,
+                                    stream, batch);
+}
+
+int sal_residual_rmsnorm_rows_f16(const void *x, const void *delta, const void *weight, void *out, void *x_out, int rows, int n,
+                                  float eps, void *stream) {
+    if (!x || !weight || !out) return SAL_E_NULL;
+    if (rows < 1 || rows > 65535 || n < 1 || n > 12000) return SAL_E_SHAPE;
+    const int threads = n >= 1024 ? 1024 : ((n + 31) / 32) * 32;
+    return launch_pdl(residual_rmsnorm_kernel, dim3(rows), dim3(threads), (size_t)n * sizeof(float), stream,
+                      reinterpret_cast<const __half *>(x), reinterpret_cast<const __half *>(delta), reinterpret_cast<const __half *>(weight),
+                      reinterpret_cast<__half *>(out), reinterpret_cast<__half *>(x_out), n, eps);
 }
 
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream) {

@@ -198,12 +198,6 @@ __device__ __forceinline__ uint32_t lds_u32_imm(uint32_t addr) {
     asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(addr), "n"(IMM));
     return v;
 }
-template <int IMM>
-__device__ __forceinline__ float4 lds_v4_imm(uint32_t addr) {   // addr + IMM must be 16-byte aligned
-    float4 v;
-    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4+%5];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr), "n"(IMM));
-    return v;
-}
 __device__ __forceinline__ void sts_f32(uint32_t addr, float v) {
     asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
@@ -517,35 +511,22 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             for (int t = 0; t < 4; ++t) pk |= (unsigned)(16 * wi + 4 * ((t + s4) & 3)) << (8 * t);
             cpack[hp][j] = pk;
         }
-    // block mode: where the lane finds the four multipliers of a weight word (one 16-byte shared load).  The
-    // multipliers of (plane, group) fill the upper half of one table row: word w of the K block at byte
-    // 128 + 16 * (w ^ phi(group)), its four chunks side by side.  phi only touches the low two bits of w, so the two
-    // half-warps (words 0-3 and 4-7) stay in different halves of the 32 banks, and it differs between the groups
-    // whose decode stores share an instruction (see store_block_mult): both directions are conflict-free.
-    unsigned mword[BLK ? 2 : 1][BLK ? 4 : 1];
+    // block mode: the same chunk offsets with the lane's group folded in, and the row of the lane's group
+    unsigned mpack[BLK ? 2 : 1][BLK ? 4 : 1];
+    uint32_t mrow = 0;
     int blk_gt = 1, blk_gshift = 0;  // column groups per tile and its log2
-    const auto blk_phi = [&](int grp) -> int {
-        if (blk_gt >= 4) {
-            const int t = (grp >> 2) & 3;
-            return ((t & 1) << 1) | (t >> 1);   // two bits reversed
-        }
-        return (grp & 1) << 1;
-    };
     if constexpr (BLK) {
         if (pr.blk_gs < BOX_COLS) {
             blk_gt = BOX_COLS / pr.blk_gs;
             blk_gshift = 31 - __clz(blk_gt);
         }
-        const int grp = pr.blk_gs < BOX_COLS ? col / pr.blk_gs : 0;
+        const unsigned grp = pr.blk_gs < BOX_COLS ? (unsigned)(col / pr.blk_gs) : 0u;
+        mrow = grp * (unsigned)LUT_ROW_BYTES;
 #pragma unroll
         for (int hp = 0; hp < 2; ++hp)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int wi = 4 * (hp ^ hw) + ((j + rot) & 3);
-                mword[hp][j] = (unsigned)(grp * LUT_ROW_BYTES + 128 + 16 * (wi ^ blk_phi(grp)));
-            }
+            for (int j = 0; j < 4; ++j) mpack[hp][j] = cpack[hp][j] ^ (0x01010101u * (4u * grp));
     }
-    const bool rot1 = (s4 & 1) != 0, rot2 = (s4 & 2) != 0;   // block mode: the lane walks the bytes of a word rotated by s4
 
     float acc[ROWS][MAX_SUB];
 #pragma unroll
@@ -579,8 +560,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     // block mode, multipliers of one tile (32 chunks x Q planes x `blk_gt` column groups), fetched by the
     // 256 consumer threads.  16/8/4 groups per tile: item e = tid + 256 i is FOUR consecutive groups
     // (one 8- or 12-byte run of alpha) of one (chunk, plane); 1 or 2 groups per tile: item = one value.
-    // The chunk bits of an item are arranged so that, with the word permutation phi, the 32 stores of a warp hit
-    // 32 different banks.
+    // The chunk bits of an item are arranged so that the 32 stores of a warp hit 32 different banks.
     constexpr int NVI = BLK ? (Q + 1) / 2 : 1;   // items per thread
     constexpr int NVW = BLK ? 3 : 1;             // 32-bit words per item (12 bytes of int8 x 3, 8 bytes of 16-bit)
     uint32_t raw_next[NVI][NVW];
@@ -662,9 +642,9 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                     }
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        sts_f32(row0 + (uint32_t)(k * LUT_ROW_BYTES + 16 * ((c >> 2) ^ blk_phi(gi + k)) + 4 * (c & 3)), decode_mult(v[k]));
+                        sts_f32(row0 + (uint32_t)(k * LUT_ROW_BYTES + 4 * (c ^ (gi + k))), decode_mult(v[k]));
                 } else {
-                    sts_f32(row0 + (uint32_t)(16 * ((c >> 2) ^ blk_phi(gi)) + 4 * (c & 3)), decode_mult(src[i][0]));
+                    sts_f32(row0 + (uint32_t)(4 * (c ^ gi)), decode_mult(src[i][0]));
                 }
             }
         }
@@ -825,9 +805,13 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                         }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        // the four multipliers of this word, per plane: one 16-byte load each (the lanes of a quad
-                        // read the same 16 bytes, a warp eight different ones in eight different bank quads)
-                        const uint32_t maddr = mword[hp][j] + mbuf + (ABS ? 0u : lut_s);
+                        // multiplier address: byte 0 <- 4 * (chunk ^ group), bytes 1.. <- row of (buffer, group)
+                        const uint32_t rowsel = mrow + mbuf;
+                        uint32_t ma[4];
+                        ma[0] = prmt(mpack[hp][j], rowsel, 0x7650u) + (ABS ? 0u : lut_s);
+                        ma[1] = prmt(mpack[hp][j], rowsel, 0x7651u) + (ABS ? 0u : lut_s);
+                        ma[2] = prmt(mpack[hp][j], rowsel, 0x7652u) + (ABS ? 0u : lut_s);
+                        ma[3] = prmt(mpack[hp][j], rowsel, 0x7653u) + (ABS ? 0u : lut_s);
 #pragma unroll
                         for (int b = 0; b < Q; ++b) {
                             const uint32_t w = wpre[j][b];
@@ -837,19 +821,19 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                                 const uint32_t off = prmt(w, cpack[hp][j], sel[t]);
                                 e[t] = ABS ? lds_u32_imm<(int)SMEM_DYNAMIC_BASE + PAR * 128>(off) : lds_u32_imm<0>(off + lut_s + PAR * 128);
                             }
-                            constexpr int MB = ABS ? (int)SMEM_DYNAMIC_BASE : 0;
-                            float4 mm;
-                            if (b == 0) mm = lds_v4_imm<MB>(maddr);
-                            else if (b == 1) mm = lds_v4_imm<MB + 1 * 16 * LUT_ROW_BYTES>(maddr);
-                            else if (b == 2) mm = lds_v4_imm<MB + 2 * 16 * LUT_ROW_BYTES>(maddr);
-                            else mm = lds_v4_imm<MB + 3 * 16 * LUT_ROW_BYTES>(maddr);
-                            // lookup t used byte (t + s4) & 3 of the word: rotate the multipliers the same way
-                            const float a0 = rot1 ? mm.y : mm.x, a1 = rot1 ? mm.z : mm.y, a2 = rot1 ? mm.w : mm.z, a3 = rot1 ? mm.x : mm.w;
-                            const float m0 = rot2 ? a2 : a0, m1 = rot2 ? a3 : a1, m2 = rot2 ? a0 : a2, m3 = rot2 ? a1 : a3;
-                            part = fmaf(m0, __uint_as_float(e[0]), part);
-                            part2 = fmaf(m1, __uint_as_float(e[1]), part2);
-                            part = fmaf(m2, __uint_as_float(e[2]), part);
-                            part2 = fmaf(m3, __uint_as_float(e[3]), part2);
+                            constexpr int MB = (ABS ? (int)SMEM_DYNAMIC_BASE : 0) + 128;
+                            float m[4];
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                if (b == 0) m[t] = lds_f32_imm<MB>(ma[t]);
+                                else if (b == 1) m[t] = lds_f32_imm<MB + 1 * 16 * LUT_ROW_BYTES>(ma[t]);
+                                else if (b == 2) m[t] = lds_f32_imm<MB + 2 * 16 * LUT_ROW_BYTES>(ma[t]);
+                                else m[t] = lds_f32_imm<MB + 3 * 16 * LUT_ROW_BYTES>(ma[t]);
+                            }
+                            part = fmaf(m[0], __uint_as_float(e[0]), part);
+                            part2 = fmaf(m[1], __uint_as_float(e[1]), part2);
+                            part = fmaf(m[2], __uint_as_float(e[2]), part);
+                            part2 = fmaf(m[3], __uint_as_float(e[3]), part2);
                         }
                     }
                     a_sub[0] += part + part2;  // the multipliers are already in

@@ -86,6 +86,35 @@ def rope_attention_decode(q, k_new, v_new, cos, sin, pos, k_cache, v_cache, out,
     return True
 
 
+def residual_rmsnorm_rows(x, delta, weight, out, x_out, eps: float):
+    """residual_rmsnorm for every row of [rows, n] tensors (one weight vector)."""
+    lib = _lib.load()
+    rows, n = x.shape[0], x.shape[1]
+    _lib.check(lib.sal_residual_rmsnorm_rows_f16(x.data_ptr(), None if delta is None else delta.data_ptr(), weight.data_ptr(),
+                                                 out.data_ptr(), None if x_out is None else x_out.data_ptr(), rows, n, float(eps),
+                                                 _stream(x)), "sal_residual_rmsnorm_rows_f16")
+
+
+def attention_workspace_batch(batch: int, heads: int, hd: int, device) -> torch.Tensor:
+    lib = _lib.load()
+    return torch.zeros(int(batch) * lib.sal_attention_workspace_bytes(int(heads), int(hd)), dtype=torch.uint8, device=device)
+
+
+def rope_attention_decode_batch(q, k_new, v_new, cos, sin, pos, k_cache, v_cache, out, heads, kv_heads, hd, scale: float, workspace):
+    """rope_attention_decode for `batch` sequences in lock step: q [batch, heads*hd], k_new / v_new [batch, kv_heads*hd] (fp16),
+    caches [batch, max_len, kv_heads, hd], out [batch, heads*hd].  Returns False — having done nothing — for shapes
+    the split kernel does not take."""
+    lib = _lib.load()
+    rc = lib.sal_rope_attention_decode_batch(q.data_ptr(), k_new.data_ptr(), v_new.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                             pos.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), q.shape[0], heads,
+                                             kv_heads, hd, k_cache.shape[1], float(scale), workspace.data_ptr(), workspace.numel(),
+                                             _stream(out))
+    if rc == _lib.SAL_E_UNSUPPORTED:
+        return False
+    _lib.check(rc, "sal_rope_attention_decode_batch")
+    return True
+
+
 def silu_mul(gate, up, out):
     lib = _lib.load()
     _lib.check(lib.sal_silu_mul_f16(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _stream(gate)),

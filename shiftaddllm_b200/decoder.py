@@ -346,12 +346,13 @@ class BcqLlamaDecoder:
 class BcqLlamaBatchDecoder:
     """Greedy decoder for `batch` sequences that advance in lock step (one shared position counter, as in a
     benchmark where all prompts have the same length).  The linear layers run as ONE small-batch LUT product
-    per group (M = batch: the weights are streamed once for all sequences); the steps between them are plain
-    torch ops, which at batch > 1 amortise their launch cost over the batch.  Weights are those of a
+    per group (M = batch: the weights are streamed once for all sequences); the steps between them are the
+    M-row forms of the fused helpers (residual + RMSNorm per row, rotary step + cache write + split attention
+    per sequence in one launch) or, with `fused=False`, plain torch ops.  Weights are those of a
     `BcqLlamaDecoder` (pass it as `like` to share them instead of drawing new ones)."""
 
     def __init__(self, shape: LlamaShape, wbits: int = 3, group_size: int = 128, max_len: int = 640, batch: int = 16,
-                 device="cuda", seed: int = 0, like: "BcqLlamaDecoder | None" = None):
+                 device="cuda", seed: int = 0, like: "BcqLlamaDecoder | None" = None, fused: bool = True):
         if not 1 <= batch <= 64:
             raise ValueError("batch must be 1..64 (rows of one small-batch LUT product)")
         self.shape, self.max_len, self.batch = shape, max_len, batch
@@ -373,6 +374,9 @@ class BcqLlamaBatchDecoder:
         self._q, self._k, self._v = torch.empty(b, h, **f16), torch.empty(b, kvh * hd, **f16), torch.empty(b, kvh * hd, **f16)
         self._o, self._down = torch.empty(b, h, **f16), torch.empty(b, h, **f16)
         self._gate, self._up = torch.empty(b, shape.ffn, **f16), torch.empty(b, shape.ffn, **f16)
+        self._x, self._hn, self._attn = torch.empty(b, h, **f16), torch.empty(b, h, **f16), torch.empty(b, h, **f16)
+        self.fused = fused
+        self._attn_ws = decode_ops.attention_workspace_batch(b, shape.heads, hd, self.device) if fused else None
         self.graph = None
 
     def _rope(self, t, heads):
@@ -383,7 +387,33 @@ class BcqLlamaBatchDecoder:
         a, c = t[:, :, 0, :], t[:, :, 1, :]
         return torch.stack((a * cos - c * sin, c * cos + a * sin), dim=2).view(b, heads, hd).half()
 
+    def _step_fused(self):
+        """The step with the M-row helpers: per block 4 small-batch LUT launches + 3 helper launches."""
+        s = self.shape
+        hd, kvh = s.head_dim, s.kv_heads
+        scale = 1.0 / math.sqrt(hd)
+        x, hn = self._x, self._hn
+        torch.index_select(self.embed, 0, self.token, out=x)
+        delta = None
+        for li, blk in enumerate(self.blocks):
+            decode_ops.residual_rmsnorm_rows(x, delta, blk.input_norm, hn, x, s.eps)
+            _group((blk.q_proj, blk.k_proj, blk.v_proj), hn, (self._q, self._k, self._v))
+            if not decode_ops.rope_attention_decode_batch(self._q, self._k, self._v, self.cos, self.sin, self.pos, self.k_cache[li],
+                                                          self.v_cache[li], self._attn, s.heads, kvh, hd, scale, self._attn_ws):
+                raise RuntimeError("this head shape is not taken by the fused attention helper: use fused=False")
+            _group((blk.o_proj,), self._attn, (self._o,))
+            decode_ops.residual_rmsnorm_rows(x, self._o, blk.post_norm, hn, x, s.eps)
+            _group((blk.gate_proj, blk.up_proj), hn, (self._gate, self._up))
+            _group((blk.down_proj,), self._gate, (self._down,), x_mul=self._up)   # SiLU(gate)*up formed in the table build
+            delta = self._down
+        decode_ops.residual_rmsnorm_rows(x, delta, self.final_norm, hn, x, s.eps)
+        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float())
+        self.token.copy_(self.logits.argmax(dim=-1))
+        self.pos.add_(1)
+
     def step(self):
+        if self.fused:
+            return self._step_fused()
         s, b = self.shape, self.batch
         hd, kvh, rep = s.head_dim, s.kv_heads, s.heads // s.kv_heads
         x = self.embed.index_select(0, self.token)                      # [b, hidden]

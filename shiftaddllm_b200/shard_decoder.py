@@ -113,7 +113,8 @@ class ColumnParallelDecoder:
         self.local = {key: [torch.empty(b, w // world, **f16) for w in ws] for key, ws in self.widths.items()}
         self._x, self._hn = torch.empty(b, h, **f16), torch.empty(b, h, **f16)
         self._attn, self._act = torch.empty(b, h, **f16), torch.empty(b, shape.ffn, **f16)
-        self._attn_ws = decode_ops.attention_workspace(shape.heads, hd, self.device) if batch == 1 else None
+        self._attn_ws = (decode_ops.attention_workspace(shape.heads, hd, self.device) if batch == 1
+                         else decode_ops.attention_workspace_batch(batch, shape.heads, hd, self.device))
         self._launches = None
         self._slot = 0
         self.graph = None
@@ -188,9 +189,7 @@ class ColumnParallelDecoder:
             if b == 1:
                 decode_ops.residual_rmsnorm(x, delta, blk.input_norm, hn, x, s.eps)
             else:
-                if delta is not None:
-                    x.add_(delta)
-                hn.copy_(F.rms_norm(x, (h,), blk.input_norm, s.eps))
+                decode_ops.residual_rmsnorm_rows(x, delta, blk.input_norm, hn, x, s.eps)
             yield from self._product(li, "qkv")
             if b == 1:
                 if not decode_ops.rope_attention_decode(q, k, v, self.cos, self.sin, self.pos, self.k_cache[li, 0], self.v_cache[li, 0],
@@ -199,8 +198,9 @@ class ColumnParallelDecoder:
                                              s.heads, kvh, hd)
                     decode_ops.attention_decode(q, self.k_cache[li, 0], self.v_cache[li, 0], self.pos, self._attn, s.heads, kvh, hd,
                                                 scale, self._attn_ws)
-            else:
-                qh, kh = self._rope(q, s.heads), self._rope(k, kvh)
+            elif not decode_ops.rope_attention_decode_batch(q, k, v, self.cos, self.sin, self.pos, self.k_cache[li], self.v_cache[li],
+                                                            self._attn, s.heads, kvh, hd, scale, self._attn_ws):
+                qh, kh = self._rope(q, s.heads), self._rope(k, kvh)       # head shapes the fused helper does not take
                 self.k_cache[li].index_copy_(1, self.pos, kh.view(b, 1, kvh, hd))
                 self.v_cache[li].index_copy_(1, self.pos, v.reshape(b, 1, kvh, hd))
                 keys = self.k_cache[li].permute(0, 2, 3, 1)
@@ -212,20 +212,18 @@ class ColumnParallelDecoder:
             if b == 1:
                 decode_ops.residual_rmsnorm(x, o_full, blk.post_norm, hn, x, s.eps)
             else:
-                x.add_(o_full)
-                hn.copy_(F.rms_norm(x, (h,), blk.post_norm, s.eps))
+                decode_ops.residual_rmsnorm_rows(x, o_full, blk.post_norm, hn, x, s.eps)
             yield from self._product(li, "gu")
             if b == 1:
                 decode_ops.silu_mul(gate, up, self._act)
             else:
-                self._act.copy_(F.silu(gate) * up)
+                decode_ops.silu_mul(gate, up, self._act)
             yield from self._product(li, "down")
             delta = down
         if b == 1:
             decode_ops.residual_rmsnorm(x, delta, self.final_norm, hn, x, s.eps)
         else:
-            x.add_(delta)
-            hn.copy_(F.rms_norm(x, (h,), self.final_norm, s.eps))
+            decode_ops.residual_rmsnorm_rows(x, delta, self.final_norm, hn, x, s.eps)
         self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float())
         self.token.copy_(self.logits.argmax(dim=-1))
         self.pos.add_(1)

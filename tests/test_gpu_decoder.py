@@ -335,9 +335,54 @@ def test_batch_decoder_matches_single_sequences():
         a, b = batch.logits[col].cpu(), single.logits.cpu()
         assert float((a - b).abs().max()) <= 2e-2 * float(b.abs().max())
         assert int(batch.token[col]) == int(single.token)
+    # the M-row helpers (default) against plain torch ops between the products: same caches, same logits
+    plain = BcqLlamaBatchDecoder(SHAPES["tiny"], max_len=32, batch=3, like=single, fused=False)
+    plain.reset()
+    plain.feed(prompts.tolist())
+    torch.cuda.synchronize()
+    assert float((plain.k_cache.float() - batch.k_cache.float()).abs().max()) <= 2e-2 * float(plain.k_cache.float().abs().max())
+    assert float((plain.logits - batch.logits).abs().max()) <= 2e-2 * float(plain.logits.abs().max())
     batch.capture()
     toks = batch.generate(3)
     assert toks.shape == (3, 3)
+
+
+@pytest.mark.parametrize("batch,heads,kvh,hd,max_len,pos_v", [(3, 8, 2, 64, 40, 17), (16, 32, 32, 128, 96, 70), (5, 64, 8, 128, 130, 0)])
+def test_lock_step_helpers_match_the_single_sequence_helpers(batch, heads, kvh, hd, max_len, pos_v):
+    """The batch forms of the norm and of rotary step + cache write + attention give, per sequence, exactly what
+    the single-sequence helpers give."""
+    from shiftaddllm_b200 import decode_ops
+
+    g = torch.Generator(device="cuda").manual_seed(batch + heads)
+    q = torch.randn(batch, heads * hd, device="cuda", generator=g).half()
+    k = torch.randn(batch, kvh * hd, device="cuda", generator=g).half()
+    v = torch.randn(batch, kvh * hd, device="cuda", generator=g).half()
+    kc = torch.randn(batch, max_len, kvh, hd, device="cuda", generator=g).half()
+    vc = torch.randn(batch, max_len, kvh, hd, device="cuda", generator=g).half()
+    inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device="cuda").float() / hd))
+    ang = torch.arange(max_len, device="cuda").float()[:, None] * inv[None, :]
+    cos, sin = ang.cos().contiguous(), ang.sin().contiguous()
+    pos = torch.tensor([pos_v], device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    kc_ref, vc_ref = kc.clone(), vc.clone()
+    out_ref = torch.empty(batch, heads * hd, dtype=torch.float16, device="cuda")
+    ws1 = decode_ops.attention_workspace(heads, hd, "cuda")
+    for b in range(batch):
+        assert decode_ops.rope_attention_decode(q[b], k[b], v[b], cos, sin, pos, kc_ref[b], vc_ref[b], out_ref[b], heads, kvh, hd, scale, ws1)
+    out = torch.empty_like(out_ref)
+    ws = decode_ops.attention_workspace_batch(batch, heads, hd, "cuda")
+    assert decode_ops.rope_attention_decode_batch(q, k, v, cos, sin, pos, kc, vc, out, heads, kvh, hd, scale, ws)
+    torch.cuda.synchronize()
+    assert torch.equal(kc, kc_ref) and torch.equal(vc, vc_ref)
+    assert float((out.float() - out_ref.float()).abs().max()) < 2e-3      # the slices per sequence differ (fewer CTAs each)
+    n = heads * hd
+    x, d = q.clone(), torch.randn(batch, n, device="cuda", generator=g).half()
+    w = (1 + 0.1 * torch.randn(n, device="cuda", generator=g)).half()
+    o1, x1, o2, x2 = (torch.empty_like(x) for _ in range(4))
+    decode_ops.residual_rmsnorm_rows(x, d, w, o1, x1, 1e-5)
+    for b in range(batch):
+        decode_ops.residual_rmsnorm(x[b:b + 1], d[b:b + 1], w, o2[b:b + 1], x2[b:b + 1], 1e-5)
+    assert torch.equal(o1, o2) and torch.equal(x1, x2)
 
 
 def test_benchmark_runs():
