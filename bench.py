@@ -86,18 +86,61 @@ def measured_peak():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples the SM clock and the clock-event (throttle) reasons of one GPU while the timed region runs.
+
+    Read-only NVML queries from a thread of this process every 2 ms (the timed region of a short run is a few
+    tens of milliseconds: too short for `nvidia-smi -lms`, whose first line alone takes longer); `nvidia-smi` in
+    a child process is the fallback where the NVML binding cannot be loaded.  `mark_begin` / `mark_end` bracket
+    the timed region on the host clock; the summary uses the samples in between and says so (or, if there are
+    none, all samples since the sampler was started right before the warm-up steps of the same loop)."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
 
     def __init__(self, index):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.thread = index, [], None, None   # rows: (host time, sm MHz, max MHz, reasons)
+        self.t0 = self.t1 = None
+        self._stop = threading.Event()
+        self.source = None
+
+    def _nvml_handle(self):
+        import pynvml
+
+        pynvml.nvmlInit()
+        try:
+            uuid = str(torch.cuda.get_device_properties(self.index).uuid)
+            return pynvml, pynvml.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:  # noqa: BLE001 - no uuid property, or not known to NVML under that name
+            return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
 
     def __enter__(self):
         try:
+            nv, handle = self._nvml_handle()
+            mx = nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM)
+            bits = ((nv.nvmlClocksEventReasonHwSlowdown, "hw_slowdown"), (nv.nvmlClocksEventReasonHwThermalSlowdown, "hw_thermal_slowdown"),
+                    (nv.nvmlClocksEventReasonSwThermalSlowdown, "sw_thermal_slowdown"), (nv.nvmlClocksEventReasonSwPowerCap, "sw_power_cap"))
+
+            def poll():
+                while not self._stop.is_set():
+                    try:
+                        sm = nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)
+                        mask = nv.nvmlDeviceGetCurrentClocksEventReasons(handle)
+                        self.rows.append((time.perf_counter(), int(sm), int(mx), [n for b, n in bits if mask & b]))
+                    except Exception:  # noqa: BLE001 - a failed query is a missing sample
+                        pass
+                    time.sleep(0.002)
+
+            self.source = "nvml"
+            self.thread = threading.Thread(target=poll, daemon=True)
+            self.thread.start()
+            return self
+        except Exception:  # noqa: BLE001 - binding or library missing: nvidia-smi below
+            pass
+        try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
                                           "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            self.source = "nvidia-smi"
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -106,21 +149,35 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            c = [v.strip() for v in line.split(",")]
+            if len(c) >= 6 and c[0].isdigit() and c[1].isdigit():
+                self.rows.append((time.perf_counter(), int(c[0]), int(c[1]), [n for n, v in zip(self.NAMES, c[2:6]) if v.startswith("Active")]))
+
+    def mark_begin(self):
+        self.t0 = time.perf_counter()
+
+    def mark_end(self):
+        self.t1 = time.perf_counter()
 
     def __exit__(self, *exc):
         if self.proc is not None:
             time.sleep(0.15)
             self.proc.terminate()
             self.proc.wait()
+        self._stop.set()
+        if self.thread is not None:
+            self.thread.join(timeout=1.0)
 
     def summary(self):
-        sm = [int(r[0]) for r in self.rows if r and r[0].isdigit()]
-        mx = [int(r[1]) for r in self.rows if len(r) > 1 and r[1].isdigit()]
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        reasons = [n for i, n in enumerate(names) if any(len(r) > 2 + i and r[2 + i].startswith("Active") for r in self.rows)]
-        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(sm)}
+        rows, window = list(self.rows), "warm-up and timed steps"
+        if self.t0 is not None and self.t1 is not None:
+            inside = [r for r in rows if self.t0 <= r[0] <= self.t1]
+            if inside:
+                rows, window = inside, "timed steps"
+        sm = [r[1] for r in rows]
+        reasons = [n for n in self.NAMES if any(n in r[3] for r in rows)]
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(r[2] for r in rows) if rows else None,
+                "reasons": reasons, "samples": len(sm), "window": window, "source": self.source}
 
 
 # ------------------------------------------------------------------------------------------
@@ -277,19 +334,22 @@ class Timer:
     def timed(self, fn, steps, warmup=None, clocks=False):
         """ms per step: CUDA events on the launch stream around `steps` calls, max over ranks."""
         with torch.cuda.stream(self.stream):
+            clk = ClockSampler(self.device.index) if clocks else None
+            if clk:
+                clk.__enter__()     # already running during the warm-up steps: no start-up gap at the timed ones
             for _ in range(max(self.args.warmup if warmup is None else warmup, 3)):
                 fn()
             self.barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            clk = ClockSampler(self.device.index) if clocks else None
             if clk:
-                clk.__enter__()
+                clk.mark_begin()
             e0.record(self.stream)
             for _ in range(steps):
                 fn()
             e1.record(self.stream)
             self.barrier()
             if clk:
+                clk.mark_end()
                 clk.__exit__()
             ms = e0.elapsed_time(e1)
         t = torch.tensor([ms], dtype=torch.float64, device=self.device)
@@ -805,7 +865,7 @@ def decode_tokens_per_s(workload, device):
     """The other half of the metric: greedy batch-1 decode of a whole decoder of the workload's
     architecture (random init, every linear a synthetic BCQ layer): 128 new tokens after a
     512-token prompt (1024 for the 70B shape), the step replayed as one CUDA graph.  Reported for
-    fixed-order fp16 GEMV outputs and for the opt-in fp32 atomic accumulation; for the 7B shape also 16
+    fixed-order fp16 GEMV outputs and for the opt-in fixed-point atomic accumulation; for the 7B shape also 16
     sequences decoded in lock step (64 new tokens each) on the small-batch kernel."""
     from shiftaddllm_b200 import decoder
 
