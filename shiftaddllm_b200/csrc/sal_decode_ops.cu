@@ -386,8 +386,11 @@ int launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, voi
 constexpr int ATTN_MAX_SPLIT = 32;
 constexpr int ATTN_WARPS = 8;
 
-// STAGE_V: the slice's V rows are fetched together with its K rows and parked in shared memory, so the
-// second pass does not wait for memory again (used when the slice fits).
+// STAGE_V: the slice's K and V rows are parked in shared memory (used when the slice fits), and the rows of EARLIER
+// positions are requested (cp.async) BEFORE the dependency wait: they were written by launches that finished
+// long ago (earlier tokens), so their trip from DRAM overlaps the tail of the kernel in front of this one.  Only the
+// newest position's row, written by this kernel (ROPE != 0) or by the rotary kernel right before it (ROPE = 0), is
+// fetched after the wait.  *pos is read before the wait for the same reason.
 // ROPE: the rotary step of the new token is done here instead of by a kernel of its own.  q is the
 // un-rotated query (rotated while it is loaded); the CTA whose slice holds position *pos rotates the new
 // key, writes it and the new value into the caches and then reads them back like any other row.
@@ -429,15 +432,16 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
     __shared__ float s_m[G], s_l[G];
     __shared__ float s_w[ATTN_MAX_SPLIT][G];
     __shared__ int s_is_last;
-    pdl_prologue();
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     constexpr int NW = ATTN_WARPS, U = 4;
     float *qf = smem_f;                  // [G][hd], pre-scaled
     float *sc = qf + G * hd;             // [G][slice_cap]
     float *obuf = sc + G * slice_cap;    // [NW][G][hd]
     uint4 *vs = reinterpret_cast<uint4 *>(obuf + NW * G * hd);   // STAGE_V: [slice_cap][hd / 8] 16-byte pieces of the V rows
+    uint4 *ks = vs + (size_t)slice_cap * (hd >> 3);              // STAGE_V: the K rows likewise
     const int kvh = blockIdx.x, split = blockIdx.y;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    int64_t pos = *pos_p;
+    int64_t pos = *pos_p;                // written by a launch that finished before this token's launches began
     const bool pos_ok = pos >= 0 && pos < max_len;
     if (pos >= max_len) pos = max_len - 1;
     if (pos < 0) pos = 0;
@@ -449,6 +453,30 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
     const int lpr_shift = 31 - __clz(lpr), hd_shift = lpr_shift + 3;
     const int rows = 32 >> lpr_shift;    // positions per warp and load instruction
     const int sub = lane >> lpr_shift, sl = lane & (lpr - 1);
+    // the slice that ends with the newest position gets that row after the wait (from this kernel's own rotary step,
+    // or from the rotary kernel in front of it); with an out-of-range *pos nothing is written and the row is an old one
+    const bool has_newest = n > 0 && t_begin + n == T;
+    const bool newest_fresh = has_newest && (ROPE == 0 || pos_ok);
+    if (STAGE_V) {
+        const int n_old = newest_fresh ? n - 1 : n;
+        const size_t stride_h = (size_t)kv_heads * hd;
+        const __half *k0 = k_cache + ((size_t)t_begin * kv_heads + kvh) * hd, *v0 = v_cache + ((size_t)t_begin * kv_heads + kvh) * hd;
+        for (int idx = tid; idx < n_old * lpr; idx += blockDim.x) {
+            const int tl = idx >> lpr_shift, piece = idx & (lpr - 1);
+            const size_t off = (size_t)tl * stride_h + piece * 8;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(ks + idx)), "l"(k0 + off) : "memory");
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(vs + idx)), "l"(v0 + off) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    if (ROPE != 0) {   // the rotary factors of this position: constant tables, asked into L1 ahead of the wait
+        const int half = hd >> 1;
+        for (int i = tid * 32; i < half; i += blockDim.x * 32) {
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(ra.cos_t + (size_t)pos * half + i));
+            asm volatile("prefetch.global.L1 [%0];" ::"l"(ra.sin_t + (size_t)pos * half + i));
+        }
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if (ROPE == 0) {
         const __half *qh = reinterpret_cast<const __half *>(q);
         for (int i = tid; i < G * hd; i += blockDim.x) qf[i] = __half2float(qh[(size_t)kvh * G * hd + i]) * scale;
@@ -465,21 +493,37 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
         }
         if (pos_ok && t_begin <= (int)pos && (int)pos < t_begin + n) {   // this CTA's slice ends with the new token
             __half *krow = k_cache + ((size_t)pos * kv_heads + kvh) * hd, *vrow = v_cache + ((size_t)pos * kv_heads + kvh) * hd;
+            // STAGE_V: the row also goes straight to its place among the staged rows
+            __half *ksrow = reinterpret_cast<__half *>(ks) + (size_t)(n - 1) * hd, *vsrow = reinterpret_cast<__half *>(vs) + (size_t)(n - 1) * hd;
             for (int j = tid; j < half; j += blockDim.x) {
                 const size_t at = (size_t)kvh * hd + j;
                 const float a = rope_in<ROPE>(ra.k_new, at), b = rope_in<ROPE>(ra.k_new, at + half);
-                krow[j] = __float2half_rn(a * cs[j] - b * sn[j]);
-                krow[half + j] = __float2half_rn(b * cs[j] + a * sn[j]);
+                const __half r0 = __float2half_rn(a * cs[j] - b * sn[j]), r1 = __float2half_rn(b * cs[j] + a * sn[j]);
+                krow[j] = r0;
+                krow[half + j] = r1;
+                if (STAGE_V) ksrow[j] = r0, ksrow[half + j] = r1;
             }
             if (ROPE == 2) __syncthreads();   // (CTA-uniform branch) the key is fully read before it is cleared
             for (int j = tid; j < hd; j += blockDim.x) {
-                vrow[j] = __float2half_rn(rope_in<ROPE>(ra.v_new, (size_t)kvh * hd + j));
+                const __half vn = __float2half_rn(rope_in<ROPE>(ra.v_new, (size_t)kvh * hd + j));
+                vrow[j] = vn;
+                if (STAGE_V) vsrow[j] = vn;
                 if (ROPE == 2) {
                     reinterpret_cast<acc_t *>(ra.k_new)[(size_t)kvh * hd + j] = 0;
                     reinterpret_cast<acc_t *>(ra.v_new)[(size_t)kvh * hd + j] = 0;
                 }
             }
         }
+    }
+    if (STAGE_V) {
+        if (ROPE == 0 && newest_fresh) {   // the row the rotary kernel in front of this one wrote
+            const size_t at = ((size_t)pos * kv_heads + kvh) * hd;
+            for (int piece = tid; piece < lpr; piece += blockDim.x) {
+                ks[(n - 1) * lpr + piece] = *reinterpret_cast<const uint4 *>(k_cache + at + piece * 8);
+                vs[(n - 1) * lpr + piece] = *reinterpret_cast<const uint4 *>(v_cache + at + piece * 8);
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
     }
     __syncthreads();   // also orders the cache rows written above before this CTA's reads of them
     const size_t row_stride = (size_t)kv_heads * hd;
@@ -497,20 +541,8 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int tl = base + u * NW * rows + sub;
-                kk[u] = tl < n ? *reinterpret_cast<const uint4 *>(kbase + (size_t)tl * row_stride) : make_uint4(0u, 0u, 0u, 0u);
-            }
-            if (STAGE_V) {
-                uint4 vv[U];
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int tl = base + u * NW * rows + sub;
-                    vv[u] = tl < n ? *reinterpret_cast<const uint4 *>(vbase + (size_t)tl * row_stride) : make_uint4(0u, 0u, 0u, 0u);
-                }
-#pragma unroll
-                for (int u = 0; u < U; ++u) {
-                    const int tl = base + u * NW * rows + sub;
-                    if (tl < n) vs[tl * lpr + sl] = vv[u];
-                }
+                if (STAGE_V) kk[u] = tl < n ? ks[tl * lpr + sl] : make_uint4(0u, 0u, 0u, 0u);
+                else kk[u] = tl < n ? *reinterpret_cast<const uint4 *>(kbase + (size_t)tl * row_stride) : make_uint4(0u, 0u, 0u, 0u);
             }
             // all U x G partial dot products first, then the butterfly over the row's lanes on all of them
             // together (independent shuffles pipeline; one value at a time they would serialise on latency)
@@ -704,7 +736,7 @@ int launch_attention_split(const void *q, const void *k_cache, const void *v_cac
                            int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap, const RopeArgs &ra,
                            cudaStream_t stream, int batch = 1, const SeqStrides &ss = SeqStrides{}) {
     const size_t base = (size_t)(G * hd + G * slice_cap + ATTN_WARPS * G * hd) * sizeof(float);
-    const size_t staged = base + (size_t)slice_cap * hd * sizeof(__half);
+    const size_t staged = base + 2 * (size_t)slice_cap * hd * sizeof(__half);   // K and V rows of a slice
     if (staged <= 96 * 1024)
         return launch_attention_variant<G, true, ROPE>(staged, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale,
                                                        workspace, nsplit, slice_cap, ra, stream, batch, ss);
