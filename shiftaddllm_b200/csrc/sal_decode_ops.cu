@@ -1,5 +1,6 @@
 // Fused element-wise / attention steps of a batch-1 decode step (see include/sal_decode_ops.h).
 // These are latency-bound helpers (a few KB each); the point is launch count, not bandwidth.
+#include <cooperative_groups.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -411,7 +412,11 @@ __device__ __forceinline__ float rope_in(const void *p, size_t i) {
     return __half2float(reinterpret_cast<const __half *>(p)[i]);
 }
 
-template <int G, bool STAGE_V, int ROPE>
+// CLUSTER (with STAGE_V, at most 8 slices): the CTAs of a kv head form a thread-block cluster and the slices are merged
+// through distributed shared memory — every CTA leaves its partial result in its own shared memory, one cluster
+// barrier, CTA 0 of the cluster reads all of them and writes the output, a second barrier keeps the others (and their
+// shared memory) alive until it has.  Replaces partials -> fence -> counter -> re-read through L2; no scratch is used.
+template <int G, bool STAGE_V, int ROPE, bool CLUSTER = false>
 __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const void *q, __half *k_cache, __half *v_cache,
                                                                           const int64_t *pos_p, __half *out, float *partial,
                                                                           unsigned *counters, int kv_heads, int hd,
@@ -653,6 +658,53 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
     __syncthreads();
     // ---- this slice's result: per query head hd unnormalised outputs, then max and sum
     const int stride = hd + 2;
+    if constexpr (CLUSTER) {
+        cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();   // (1, nsplit, 1): rank = split
+        float *pbuf = reinterpret_cast<float *>(ks + (size_t)slice_cap * lpr);            // [G][hd + 2]
+        for (int i = tid; i < G * hd; i += blockDim.x) {
+            const int g = i >> hd_shift, d = i & (hd - 1);
+            float r = 0.f;
+#pragma unroll
+            for (int w = 0; w < NW; ++w) r += obuf[(w * G + g) * hd + d];
+            pbuf[g * stride + d] = r;
+        }
+        if (tid < G) {
+            pbuf[tid * stride + hd] = s_m[tid];
+            pbuf[tid * stride + hd + 1] = s_l[tid];
+        }
+        cluster.sync();
+        if (split == 0) {
+            for (int g = warp; g < G; g += NW) {
+                float m_sp = -INFINITY, l_sp = 0.f;
+                if (lane < nsplit) {
+                    const float *ps = cluster.map_shared_rank(pbuf, lane) + g * stride;
+                    m_sp = ps[hd];
+                    l_sp = ps[hd + 1];
+                }
+                const float m = warp_max(m_sp);
+                const float wgt = lane < nsplit ? __expf(m_sp - m) : 0.f;
+                const float l = warp_sum(wgt * l_sp);
+                if (lane < nsplit) s_w[lane][g] = wgt / l;
+            }
+            __syncthreads();
+            for (int i = tid; i < G * hd; i += blockDim.x) {
+                const int g = i >> hd_shift, d = i & (hd - 1);
+                float t[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) t[k] = k < nsplit ? cluster.map_shared_rank(pbuf, k)[g * stride + d] : 0.f;
+                float acc = 0.f;
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc += k < nsplit ? s_w[k][g] * t[k] : 0.f;
+                out[((size_t)kvh * G + g) * hd + d] = __float2half_rn(acc);
+            }
+            if (ROPE == 2) {   // every CTA of this kv head has passed the barrier, hence has read the query accumulators
+                acc_t *qacc = reinterpret_cast<acc_t *>(const_cast<void *>(q));
+                for (int i = tid; i < G * hd; i += blockDim.x) qacc[(size_t)kvh * G * hd + i] = 0;
+            }
+        }
+        cluster.sync();   // nobody leaves while its partial result may still be read
+        return;
+    }
     float *mine = partial + ((size_t)(kvh * nsplit + split) * G) * stride;
     for (int i = tid; i < G * hd; i += blockDim.x) {
         const int g = i >> hd_shift, d = i & (hd - 1);
@@ -708,7 +760,7 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
 
 constexpr size_t ATTN_WS_HEADER = 1024;   // arrival counters, one per kv head (<= 256 heads)
 
-template <int G, bool STAGE_V, int ROPE>
+template <int G, bool STAGE_V, int ROPE, bool CLUSTER = false>
 int launch_attention_variant(size_t smem, const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
                              int kv_heads, int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap,
                              const RopeArgs &ra, cudaStream_t stream, int batch = 1, const SeqStrides &ss = SeqStrides{}) {
@@ -718,25 +770,73 @@ int launch_attention_variant(size_t smem, const void *q, const void *k_cache, co
         int dev = 0;
         if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SAL_E_DEVICE;
         if (configured[dev] < smem) {
-            if (cudaFuncSetAttribute(attention_split_kernel<G, STAGE_V, ROPE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            if (cudaFuncSetAttribute(attention_split_kernel<G, STAGE_V, ROPE, CLUSTER>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem) != cudaSuccess)
                 return SAL_E_LAUNCH;
             configured[dev] = smem;
         }
     }
-    return launch_pdl(attention_split_kernel<G, STAGE_V, ROPE>, dim3(kv_heads, nsplit, batch), dim3(ATTN_WARPS * 32), smem, stream, q,
+    if (CLUSTER) {   // the slices of a kv head are one thread-block cluster (at most 8: the portable size)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kv_heads, nsplit, batch);
+        cfg.blockDim = dim3(ATTN_WARPS * 32);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        attr[1].id = cudaLaunchAttributeClusterDimension;
+        attr[1].val.clusterDim.x = 1;
+        attr[1].val.clusterDim.y = (unsigned)nsplit;
+        attr[1].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 2;
+        {   // once per device and cluster shape: can such a cluster be resident at all?  If not, the caller takes the other merge.
+            static signed char fits[64][9];
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || nsplit > 8) return SAL_E_DEVICE;
+            if (fits[dev][nsplit] == 0) {
+                int clusters = 0;
+                const cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, attention_split_kernel<G, STAGE_V, ROPE, CLUSTER>, &cfg);
+                if (e != cudaSuccess) (void)cudaGetLastError();
+                fits[dev][nsplit] = (e == cudaSuccess && clusters >= 1) ? 1 : -1;
+            }
+            if (fits[dev][nsplit] < 0) return SAL_E_UNSUPPORTED;
+        }
+        return cudaLaunchKernelEx(&cfg, attention_split_kernel<G, STAGE_V, ROPE, CLUSTER>, q,
+                                  reinterpret_cast<__half *>(const_cast<void *>(k_cache)),
+                                  reinterpret_cast<__half *>(const_cast<void *>(v_cache)), pos, reinterpret_cast<__half *>(out),
+                                  reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + ATTN_WS_HEADER),
+                                  reinterpret_cast<unsigned *>(workspace), kv_heads, hd, max_len, scale, nsplit, slice_cap, ra,
+                                  ss) == cudaSuccess
+                   ? SAL_OK
+                   : SAL_E_LAUNCH;
+    }
+    return launch_pdl(attention_split_kernel<G, STAGE_V, ROPE, CLUSTER>, dim3(kv_heads, nsplit, batch), dim3(ATTN_WARPS * 32), smem, stream, q,
                       reinterpret_cast<__half *>(const_cast<void *>(k_cache)), reinterpret_cast<__half *>(const_cast<void *>(v_cache)),
                       pos, reinterpret_cast<__half *>(out),
                       reinterpret_cast<float *>(reinterpret_cast<char *>(workspace) + ATTN_WS_HEADER),
                       reinterpret_cast<unsigned *>(workspace), kv_heads, hd, max_len, scale, nsplit, slice_cap, ra, ss);
 }
 
+// Shared memory of one CTA: query, scores, per-warp outputs; staged: K and V rows of a slice; cluster: its partial result.
+inline size_t attn_smem_base(int G, int hd, int slice_cap) { return (size_t)(G * hd + G * slice_cap + ATTN_WARPS * G * hd) * sizeof(float); }
+inline size_t attn_smem_staged(int G, int hd, int slice_cap) { return attn_smem_base(G, hd, slice_cap) + 2 * (size_t)slice_cap * hd * sizeof(__half); }
+inline size_t attn_smem_cluster(int G, int hd, int slice_cap) { return attn_smem_staged(G, hd, slice_cap) + (size_t)G * (hd + 2) * sizeof(float); }
+constexpr size_t ATTN_CLUSTER_SMEM_MAX = 160 * 1024;
+
 template <int G, int ROPE>
 int launch_attention_split(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out, int kv_heads,
                            int hd, int max_len, float scale, void *workspace, int nsplit, int slice_cap, const RopeArgs &ra,
-                           cudaStream_t stream, int batch = 1, const SeqStrides &ss = SeqStrides{}) {
-    const size_t base = (size_t)(G * hd + G * slice_cap + ATTN_WARPS * G * hd) * sizeof(float);
-    const size_t staged = base + 2 * (size_t)slice_cap * hd * sizeof(__half);   // K and V rows of a slice
+                           cudaStream_t stream, int batch = 1, const SeqStrides &ss = SeqStrides{}, bool cluster = false) {
+    const size_t base = attn_smem_base(G, hd, slice_cap);
+    const size_t staged = attn_smem_staged(G, hd, slice_cap);
+    if (cluster) {   // the caller has checked that the staged rows fit
+        const int rc = launch_attention_variant<G, true, ROPE, true>(attn_smem_cluster(G, hd, slice_cap), q, k_cache, v_cache, pos, out,
+                                                                     kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, stream,
+                                                                     batch, ss);
+        if (rc != SAL_E_UNSUPPORTED) return rc;   // unsupported: no such cluster can be resident here; merge through L2 instead
+    }
     if (staged <= 96 * 1024)
         return launch_attention_variant<G, true, ROPE>(staged, q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale,
                                                        workspace, nsplit, slice_cap, ra, stream, batch, ss);
@@ -765,7 +865,19 @@ int attention_split_entry(const void *q, const void *k_cache, const void *v_cach
     if (nsplit < 1) nsplit = 1;
     // capacity of a slice, rounded up to a multiple of 4: the staged V rows behind the G x slice_cap scores in
     // shared memory are written with 16-byte stores
-    const int slice_cap = ((max_len + nsplit - 1) / nsplit + 3) & ~3;
+    int slice_cap = ((max_len + nsplit - 1) / nsplit + 3) & ~3;
+    // Up to 8 slices whose K and V rows fit into shared memory: the slices of a kv head run as one thread-block
+    // cluster and are merged through distributed shared memory (longer contexts keep the merge through L2).
+    bool cluster = false;
+    if (nsplit > 1) {
+        const int ns_c = nsplit < 8 ? nsplit : 8;
+        const int cap_c = ((max_len + ns_c - 1) / ns_c + 3) & ~3;
+        if (attn_smem_cluster(heads / kv_heads, hd, cap_c) <= ATTN_CLUSTER_SMEM_MAX) {
+            cluster = true;
+            nsplit = ns_c;
+            slice_cap = cap_c;
+        }
+    }
     cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
     // sequences in lock step: operands of sequence z lie z rows / caches / scratch blocks further on
     const size_t qelem = ROPE == 2 ? sizeof(acc_t) : sizeof(__half);
@@ -778,10 +890,10 @@ int attention_split_entry(const void *q, const void *k_cache, const void *v_cach
         ss.scratch = ws_seq;
     }
     switch (G) {
-        case 1: return launch_attention_split<1, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
-        case 2: return launch_attention_split<2, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
-        case 4: return launch_attention_split<4, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
-        case 8: return launch_attention_split<8, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss);
+        case 1: return launch_attention_split<1, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss, cluster);
+        case 2: return launch_attention_split<2, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss, cluster);
+        case 4: return launch_attention_split<4, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss, cluster);
+        case 8: return launch_attention_split<8, ROPE>(q, k_cache, v_cache, pos, out, kv_heads, hd, max_len, scale, workspace, nsplit, slice_cap, ra, s, batch, ss, cluster);
         default: return SAL_E_UNSUPPORTED;
     }
 }
