@@ -60,6 +60,7 @@ constexpr int WS_COUNTER_BYTES = 16384 - WS_HEADER_BYTES;
 constexpr int WS_MAX_COUNTERS = WS_COUNTER_BYTES / 4;
 constexpr size_t WS_PARTIAL_OFFSET = 16384;
 constexpr int BOX_COLS = 256;             // columns of one TMA box (the limit of a tensor-map box dimension)
+constexpr int ACT_BYTES = KB_FEATS * 2;   // one K block of fp16 activations, staged by the SwiGLU variants (M = 1)
 
 enum AlphaKind { A_ROW_F16 = 0, A_ROW_HALVING = 1, B_F16 = 2, B_U16 = 3, B_I8 = 4 };
 
@@ -244,6 +245,19 @@ __device__ __forceinline__ void build_tables_impl(const __half *__restrict__ x0,
     float xf[ROWS][8];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r) {
+        if (SWIGLU == 4) {
+            // the K block's activations were formed once per CTA and staged in shared memory as fp16 (x0 = their
+            // generic address); lane = chunk takes its eight
+            const uint4 raw = *(reinterpret_cast<const uint4 *>(x0) + lane);
+            const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                xf[r][2 * i] = f.x;
+                xf[r][2 * i + 1] = f.y;
+            }
+            continue;
+        }
         if (SWIGLU == 2) {
             // gate and up are the fixed-point accumulators two earlier products added into (plain loads: they were
             // written by atomics of the previous kernels, not constant data)
@@ -388,6 +402,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     const uint32_t full0 = smem_u32(bars);
     const uint32_t empty0 = smem_u32(bars + stages);
     volatile int &s_last = *reinterpret_cast<volatile int *>(bars + 2 * stages);
+    __half *act_s = reinterpret_cast<__half *>(bars + 2 * stages + 2);   // ACT_BYTES, 16-byte aligned
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
@@ -473,6 +488,26 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     auto build_block = [&](int kb, int half, int w, auto nwarps_tag) {
         constexpr int NW = decltype(nwarps_tag)::value;
         const size_t ko = (size_t)kb * KB_FEATS;
+        if (SWIGLU != 0 && ROWS == 1) {
+            // silu(gate) * up of the K block's 256 features, ONE per consumer thread, staged as fp16; the warps then build
+            // from the staged values.  (Each warp forming all 256 itself, as the plain-activation path does with its
+            // single 16-byte load, costs eight times the conversions, exponentials and divisions.)  Rounded step by
+            // step exactly as the separate element-wise kernel (and torch's fp16 ops) would round.
+            float gi, ui;
+            if (SWIGLU == 2) {   // 64-bit fixed-point accumulators written by the atomics of earlier kernels: plain loads
+                const long long *gp = reinterpret_cast<const long long *>(pr.x) + ko, *up = reinterpret_cast<const long long *>(pr.x_mul) + ko;
+                gi = __half2float(__float2half_rn(from_fixed(gp[tid])));
+                ui = __half2float(__float2half_rn(from_fixed(up[tid])));
+            } else {
+                gi = __half2float(pr.x[ko + tid]);
+                ui = __half2float(pr.x_mul[ko + tid]);
+            }
+            const float sg = __half2float(__float2half_rn(gi / (1.f + __expf(-gi))));
+            act_s[tid] = __float2half_rn(sg * ui);
+            consumer_barrier(NCW * 32);
+            build_tables_impl<NW, 1, 4>(act_s, nullptr, nullptr, nullptr, lut_s + half * 128, w, lane);
+            return;
+        }
         if (SWIGLU == 2) {   // 64-bit fixed-point operands: same element offsets, four times the bytes (pointers are carried as __half*)
             const __half *g32 = pr.x + 4 * ((xrow0 - pr.x) + ko);
             const __half *u32 = pr.x_mul + 4 * ((xrow0 - pr.x) + ko);
@@ -1329,13 +1364,13 @@ int choose_stages(int q, int ncw, int smem_optin, int *smem_bytes) {
     const int sb = stage_bytes_for(q, ncw);
     const bool whole_sm = g_full_sm || ncw > 8;
     const int per_cta = whole_sm ? smem_optin : (smem_optin + 1024) / 2 - 1024;  // each resident CTA also reserves 1 KB
-    int budget = per_cta - LUT_BYTES - 256;              // barriers and the reduction flag
+    int budget = per_cta - LUT_BYTES - 256 - ACT_BYTES;  // barriers, the reduction flag, one K block of staged activations
     int stages = budget / sb;
     if (stages > 8) stages = 8;
     if (g_stage_override > 0 && g_stage_override < stages) stages = g_stage_override;
     if (stages < q / planes_per_slot(q)) stages = q / planes_per_slot(q) <= budget / sb ? q / planes_per_slot(q) : 0;
     if (stages < 1) return 0;
-    *smem_bytes = LUT_BYTES + stages * sb + 2 * stages * 8 + 16;   // tables, ring, its barriers, a flag
+    *smem_bytes = LUT_BYTES + stages * sb + 2 * stages * 8 + 16 + ACT_BYTES;   // tables, ring, its barriers, a flag, staged activations
     return stages;
 }
 
