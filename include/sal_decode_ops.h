@@ -50,11 +50,19 @@ int sal_attention_decode_f16(const void *q, const void *k_cache, const void *v_c
                              int heads, int kv_heads, int hd, int max_len, float scale, void *stream);
 
 /* The same attention split over the cached positions (kv_heads x up to 32 CTAs instead of one CTA per head;
- * a K / V row is read once for all query heads of its group) with the slices merged by the last CTA of a
- * kv head to finish.  hd in {32, 64, 128, 256}, heads / kv_heads in {1, 2, 4, 8}, caches 16-byte aligned;
+ * a K / V row is read once for all query heads of its group).  Where the K and V rows of a slice fit into
+ * shared memory (up to 8 slices), the slices of a kv head run as one thread-block cluster and are merged through
+ * distributed shared memory; longer contexts are merged through the scratch buffer by the last CTA of a kv head to
+ * finish.  hd in {32, 64, 128, 256}, heads / kv_heads in {1, 2, 4, 8}, caches 16-byte aligned;
  * other shapes return SAL_E_UNSUPPORTED (use sal_attention_decode_f16).  `workspace`: caller-owned scratch of
  * sal_attention_workspace_bytes(heads, hd) bytes, zero-filled once (arrival counters reset themselves), not
- * shared between streams. */
+ * shared between streams.
+ * Ordering contract of the split kernels (this one, sal_rope_attention_decode and its batch form): they are
+ * launched with programmatic dependent launch and read *pos and the cache rows of positions BEFORE *pos ahead of
+ * their dependency wait, so that those rows are already on their way while the kernel in front drains.  These
+ * must therefore be complete when the launch DIRECTLY in front of this one starts — true whenever they were
+ * written by an earlier token's launches and the token boundary holds at least one ordinary (fully serialising)
+ * launch or a synchronisation, as any sampler does.  Row *pos itself, q and k_new / v_new are read after the wait. */
 size_t sal_attention_workspace_bytes(int heads, int hd);
 int sal_attention_decode_split_f16(const void *q, const void *k_cache, const void *v_cache, const int64_t *pos, void *out,
                                    int heads, int kv_heads, int hd, int max_len, float scale, void *workspace,
@@ -82,6 +90,12 @@ int sal_residual_rmsnorm_rows_f16(const void *x, const void *delta, const void *
 int sal_rope_attention_decode_batch(void *q, void *k_new, void *v_new, const void *cos, const void *sin, const int64_t *pos,
                                     void *k_cache, void *v_cache, void *out, int batch, int heads, int kv_heads, int hd, int max_len,
                                     float scale, void *workspace, size_t workspace_bytes, void *stream);
+
+/* End of a greedy decode step in one launch: logits_f16 [vocab] (as an fp16 lm_head product leaves them) are copied
+ * to logits_f32 (may be NULL), *token = index of the largest logit (the smallest index among equal maxima, as
+ * torch.argmax; NaNs are never selected) and *pos += 1.  Replaces the convert / copy / argmax / copy / add
+ * operators a framework runs there.  vocab % 8 == 0, logits_f16 16-byte aligned. */
+int sal_greedy_token_f16(const void *logits_f16, void *logits_f32, int vocab, int64_t *token, int64_t *pos, void *stream);
 
 /* out = silu(gate) * up, fp16 vectors of n elements. */
 int sal_silu_mul_f16(const void *gate, const void *up, void *out, int n, void *stream);

@@ -78,6 +78,7 @@ SIGNATURES = {
     "sal_rope_attention_decode": (_i, [_vp, _vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, ctypes.c_float, _vp,
                                        ctypes.c_size_t, _vp]),
     "sal_silu_mul_f16": (_i, [_vp, _vp, _vp, _i, _vp]),
+    "sal_greedy_token_f16": (_i, [_vp, _vp, _i, _vp, _vp, _vp]),
     "sal_residual_rmsnorm_rows_f16": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, ctypes.c_float, _vp]),
     "sal_rope_attention_decode_batch": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, ctypes.c_float, _vp,
                                             ctypes.c_size_t, _vp]),

@@ -238,6 +238,9 @@ struct TileCfg {
 // entries (entry >> 3 = hg).  Bank of every store = lane.  ROWS = 1: fp32 entries of activation
 // row x0.  ROWS = 2: half2 entries, low half = row x0, high half = row x1 (sums are formed in
 // fp32 and rounded once).
+template <int NCW, int ROWS>
+__device__ __forceinline__ void store_tables(const float (&xf)[ROWS][8], uint32_t lut_half, int warp, int lane);
+
 template <int NCW, int ROWS, int SWIGLU>
 __device__ __forceinline__ void build_tables_impl(const __half *__restrict__ x0, const __half *__restrict__ x1,
                                                   const __half *__restrict__ m0, const __half *__restrict__ m1,
@@ -298,6 +301,11 @@ __device__ __forceinline__ void build_tables_impl(const __half *__restrict__ x0,
             }
         }
     }
+    store_tables<NCW, ROWS>(xf, lut_half, warp, lane);
+}
+
+template <int NCW, int ROWS>
+__device__ __forceinline__ void store_tables(const float (&xf)[ROWS][8], uint32_t lut_half, int warp, int lane) {
     float low[ROWS][8];
 #pragma unroll
     for (int r = 0; r < ROWS; ++r)
@@ -506,6 +514,30 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             act_s[tid] = __float2half_rn(sg * ui);
             consumer_barrier(NCW * 32);
             build_tables_impl<NW, 1, 4>(act_s, nullptr, nullptr, nullptr, lut_s + half * 128, w, lane);
+            return;
+        }
+        if (SWIGLU == 1 && ROWS == 2) {
+            // the same for a pair of rows, one after the other through the one staging buffer
+            float xf[2][8];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const __half *grow = (r == 0 ? xrow0 : xrow1) + ko;
+                const __half *urow = pr.x_mul + (grow - pr.x);   // x_mul row = x_mul + (the same element offset the x row has)
+                const float gi = __half2float(grow[tid]);
+                const float sg = __half2float(__float2half_rn(gi / (1.f + __expf(-gi))));
+                act_s[tid] = __float2half_rn(sg * __half2float(urow[tid]));
+                consumer_barrier(NCW * 32);
+                const uint4 raw = *(reinterpret_cast<const uint4 *>(act_s) + lane);
+                const __half2 *h = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(h[i]);
+                    xf[r][2 * i] = f.x;
+                    xf[r][2 * i + 1] = f.y;
+                }
+                if (r == 0) consumer_barrier(NCW * 32);   // everybody has its eight before the second row overwrites them
+            }
+            store_tables<NW, 2>(xf, lut_s + half * 128, w, lane);
             return;
         }
         if (SWIGLU == 2) {   // 64-bit fixed-point operands: same element offsets, four times the bytes (pointers are carried as __half*)

@@ -115,6 +115,18 @@ def rope_attention_decode_batch(q, k_new, v_new, cos, sin, pos, k_cache, v_cache
     return True
 
 
+def greedy_token(logits_f16, logits_f32, token, pos):
+    """End of a greedy step in one launch: fp32 copy of the fp16 logits (``logits_f32`` may be None), ``token[0]`` =
+    argmax (first of equal maxima), ``pos[0] += 1``.  False if the vocabulary size is not a multiple of 8."""
+    vocab = logits_f16.numel()
+    if vocab % 8 != 0 or logits_f16.dtype != torch.float16 or not logits_f16.is_contiguous():
+        return False
+    lib = _lib.load()
+    _lib.check(lib.sal_greedy_token_f16(logits_f16.data_ptr(), logits_f32.data_ptr() if logits_f32 is not None else None, vocab,
+                                        token.data_ptr(), pos.data_ptr(), _stream(logits_f16)), "sal_greedy_token_f16")
+    return True
+
+
 def silu_mul(gate, up, out):
     lib = _lib.load()
     _lib.check(lib.sal_silu_mul_f16(gate.data_ptr(), up.data_ptr(), out.data_ptr(), gate.numel(), _stream(gate)),

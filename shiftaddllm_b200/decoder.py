@@ -200,9 +200,16 @@ class BcqLlamaDecoder:
             _group((blk.down_proj,), self._gate, (self._down,), x_mul=self._up)   # SiLU(gate)*up formed in the table build
             delta = self._down
         decode_ops.residual_rmsnorm(x, delta, self.final_norm, hn, x, s.eps)
-        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
-        self.token.copy_(self.logits.argmax().view(1))
-        self.pos.add_(1)
+        self._finish(hn)
+
+    def _finish(self, hn):
+        """fp16 `lm_head` product, then fp32 logits, greedy token and position + 1 in one helper launch (torch
+        operators where the helper does not take the vocabulary size)."""
+        lg = torch.matmul(hn, self.lm_head.t()).view(-1)
+        if not decode_ops.greedy_token(lg, self.logits, self.token, self.pos):
+            self.logits.copy_(lg.float())
+            self.token.copy_(self.logits.argmax().view(1))
+            self.pos.add_(1)
 
     def set_atomic(self, atomic: bool):
         """Switches between fp16 outputs reduced in fixed order and fixed-point atomic accumulation (drops a captured graph)."""
@@ -238,9 +245,7 @@ class BcqLlamaDecoder:
             _group((blk.down_proj,), self._gateacc, (self._downacc,), x_mul=self._upacc, atomic=True, swiglu_fixed=True)
             delta = self._downacc
         decode_ops.residual_rmsnorm_fixedacc(x, delta, self.final_norm, hn, x, s.eps, self._gateacc, self._upacc)
-        self.logits.copy_(torch.matmul(hn, self.lm_head.t()).float().view(-1))
-        self.token.copy_(self.logits.argmax().view(1))
-        self.pos.add_(1)
+        self._finish(hn)
 
     def capture(self):
         """Captures `step` in a CUDA graph (one eager warm-up step first: it sizes the workspace and

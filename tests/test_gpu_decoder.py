@@ -389,3 +389,33 @@ def test_benchmark_runs():
     model = BcqLlamaDecoder(SHAPES["tiny"], wbits=3, max_len=96, seed=3)
     res = benchmark(model, prompt_len=16, new_tokens=8, warmup=2)
     assert res["tokens_per_s"] > 0 and res["new_tokens"] == 8
+
+
+@pytest.mark.parametrize("vocab", [1000, 32000, 8])
+def test_greedy_token_helper(vocab):
+    """fp32 copy of the logits, the first of equal maxima (as torch.argmax), position + 1; NaNs are never chosen."""
+    from shiftaddllm_b200 import decode_ops
+
+    gen = torch.Generator(device="cuda").manual_seed(vocab)
+    for trial in range(4):
+        lg = torch.randn(vocab, device="cuda", generator=gen).half()
+        if trial == 1:      # several equal maxima, the first one not in the first thread's share
+            top = lg.max() + 1
+            for i in (vocab - 1, vocab // 2, vocab // 3):
+                lg[i] = top
+        if trial == 2:
+            lg[0] = float("nan")
+        if trial == 3:
+            lg.fill_(-3.0)      # all equal: index 0
+        out32 = torch.zeros(vocab, dtype=torch.float32, device="cuda")
+        token = torch.full((1,), -1, dtype=torch.long, device="cuda")
+        pos = torch.full((1,), 41, dtype=torch.long, device="cuda")
+        assert decode_ops.greedy_token(lg, out32, token, pos)
+        torch.cuda.synchronize()
+        ref = lg.float()
+        assert torch.equal(out32.nan_to_num(7.0), ref.nan_to_num(7.0))
+        want = int(torch.where(ref.isnan(), torch.full_like(ref, -float("inf")), ref).argmax())
+        if trial in (1, 3):
+            want = vocab // 3 if trial == 1 else 0
+        assert int(token) == want and int(pos) == 42
+    assert not decode_ops.greedy_token(torch.zeros(12, dtype=torch.float16, device="cuda"), None, token, pos)
