@@ -20,6 +20,7 @@ user calls, with the activations coming from pinned host memory and the results 
 inside the timed region.  `verify` = what the timed launches computed, compared after the timed
 region with a plain fp32 torch dequantise-and-matmul on sampled output columns.  Further legs
 (each a sub-record of the same line; `--legs` selects):
+  overlapped_launches  the headline launches issued alternately on two streams (informational)
   small_batch  the same 7B shapes with per-layer bit widths drawn from {2,3,4} (p = 0.3/0.5/0.2)
                at M in {1,4,8,16,64}: the small-batch variant of the kernel
   block_int8   the 7B shapes in the layout of the published "Lat." checkpoints (one int8 power-of-two
@@ -62,7 +63,7 @@ G = 128
 BLOCK_GS = 16          # columns per multiplier of the block ("Lat." g128) layout: groupsize / 8
 HEADLINE_GROUPS = [[0, 1, 2, 3, 4, 5, 6]]
 DEPENDENCY_GROUPS = [[0, 1, 2], [3], [4, 5], [6]]
-ALL_LEGS = ("verify", "e2e", "dependency_ordered", "small_batch", "block_int8", "config5", "decode", "cpu_baseline",
+ALL_LEGS = ("verify", "e2e", "overlapped_launches", "dependency_ordered", "small_batch", "block_int8", "config5", "decode", "cpu_baseline",
             "reference_gpu_kernel")
 
 
@@ -416,6 +417,25 @@ class SetRunner:
                 launch()
                 dist.all_gather_into_tensor(full, local)
 
+    def step_two_streams(self, side):
+        """The same launches with the even ones on the current stream and the odd ones on `side` (one GPU; the
+        products of different launches are independent, each stream has its own scratch buffer): a launch no longer
+        waits for the last thread block of the launch in front of it, only for the one before that."""
+        from shiftaddllm_b200 import lutgemm
+
+        if getattr(self, "_split", None) is None:
+            self._split = (lutgemm.LaunchSequence(self.prepared[0::2]), lutgemm.LaunchSequence(self.prepared[1::2]))
+        cur = torch.cuda.current_stream()
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        side.wait_event(fork)
+        with torch.cuda.stream(side):
+            self._split[1]()
+            join = torch.cuda.Event()
+            join.record(side)
+        self._split[0]()
+        cur.wait_event(join)
+
     def exchange_check(self):
         """After a step: the gather buffer of every launch against an NCCL all-gather of the local slices."""
         import torch.distributed as dist
@@ -531,6 +551,25 @@ def run_ours(args, rank, world, device):
                              "checker": "fp32 torch dequantise + matmul on the same device tensors"}
             if world > 1:
                 out["exchange_check"] = head.exchange_check()
+
+    # ---- the same launches issued alternately on two streams (informational: shows what the wait for the last thread
+    # block of the launch in front costs a chain of launches)
+    if "overlapped_launches" in legs and world == 1:
+        side = torch.cuda.Stream(device)
+        two_replay, two_graphed = timer.capture(lambda: head.step_two_streams(side))
+        two_ms, _ = timer.timed(two_replay, args.steps)
+        rec = {"ms_per_step": round(two_ms, 4), "value": round(total / (two_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
+               "frac_of_measured_hbm": round(total / (two_ms * 1e-3) / 1e9 / peak, 4),
+               "structure": "the headline launches, even ones on one stream and odd ones on a second (each PDL chained, own "
+                            "scratch buffer), " + ("one CUDA graph" if two_graphed else "eager")}
+        if "verify" in legs:
+            with torch.cuda.stream(stream):
+                lset.y_all.zero_()
+                two_replay()
+                torch.cuda.synchronize(device)
+                rec["verify_max_rel_err"] = round(verify_products([p for prods in (head.products[0], head.products[1], head.products[-1])
+                                                                   for p in prods], device), 6)
+        out["overlapped_launches"] = rec
 
     # ---- the same step in the order a decoder's data dependencies force
     dep = None
@@ -750,6 +789,15 @@ def sharded_decoder_record(args, rank, world, device):
         ms = max_over_ranks(r["ms_per_step"])
         rec[f"batch{batch}"] = {"tokens_per_s": round(batch * 1e3 / ms, 1), "ms_per_step": round(ms, 4), "prompt": fill,
                                 "exchange": "fused into the GEMV kernels" if model.fused else ("NCCL all-gather" if world > 1 else "none")}
+        del model
+        torch.cuda.empty_cache()
+    if world == 1:
+        # what one GPU is best at: no exchange, so the products can add into fixed-point accumulators (no split-K tail)
+        model = decoder.BcqLlamaDecoder(shape, 2, G, max_len=prompt + 2 * new + 16, device=device, atomic=True)
+        r = decoder.benchmark(model, prompt, new)
+        rec["batch1_fixed_accumulators"] = {"tokens_per_s": round(r["tokens_per_s"], 1), "ms_per_step": round(r["ms_per_token"], 4),
+                                            "prompt": "prompt fed through the model in chunks of 64 tokens",
+                                            "structure": "single-GPU decoder, products add into 64-bit fixed-point accumulators"}
         del model
         torch.cuda.empty_cache()
     return rec
