@@ -116,11 +116,13 @@ def test_fused_helpers_match_torch():
 
 @pytest.mark.parametrize("heads,kvh,hd,max_len,pos_v", [(8, 2, 64, 40, 17), (32, 32, 128, 784, 600), (64, 8, 128, 1296, 1100),
                                                         (4, 4, 32, 16, 0), (16, 2, 128, 300, 299), (8, 4, 256, 64, 33),
-                                                        (8, 8, 128, 601, 600), (4, 4, 64, 203, 77)])
+                                                        (8, 8, 128, 601, 600), (4, 4, 64, 203, 77),
+                                                        (8, 8, 128, 4096, 3000), (32, 32, 128, 8192, 5000), (16, 2, 64, 8192, 8191)])
 def test_split_attention_matches_torch(heads, kvh, hd, max_len, pos_v):
-    """Attention split over the cached positions (one CTA per kv head and slice, merged by the last
-    one to finish) against torch, for plain and grouped-query layouts, and run twice on one scratch
-    buffer (the arrival counters must have reset themselves)."""
+    """Attention split over the cached positions against torch, for plain and grouped-query layouts, and run twice
+    on one scratch buffer (the arrival counters of the merge through L2 must have reset themselves).  Short caches
+    take the cluster merge through distributed shared memory; 4096 positions on 8 kv heads the staged rows with
+    the merge through L2; 8192 positions the rows read from global memory after the dependency wait."""
     from shiftaddllm_b200 import decode_ops
 
     g = torch.Generator(device="cuda").manual_seed(heads * 1000 + pos_v)
@@ -143,7 +145,8 @@ def test_split_attention_matches_torch(heads, kvh, hd, max_len, pos_v):
 
 
 @pytest.mark.parametrize("heads,kvh,hd,max_len,pos_v,f32", [(8, 2, 64, 40, 17, False), (32, 32, 128, 200, 150, True),
-                                                            (64, 8, 128, 300, 0, True), (8, 8, 32, 64, 63, False)])
+                                                            (64, 8, 128, 300, 0, True), (8, 8, 32, 64, 63, False),
+                                                            (8, 8, 128, 4096, 3000, True), (32, 32, 128, 8192, 5000, False)])
 def test_rope_attention_fused_equals_two_kernels(heads, kvh, hd, max_len, pos_v, f32):
     """Rotary step + cache write + attention in one kernel against the two separate helpers:
     same cache contents and the same output; fixed-point accumulator inputs are consumed and cleared."""
