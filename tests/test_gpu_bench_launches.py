@@ -183,3 +183,30 @@ def test_prepared_launch_through_the_c_abi():
     lib.sal_destroy_prepared(handle)
     lib.sal_destroy_prepared(second)
     check_products(flat)
+
+
+def test_two_stream_issue_gives_the_same_results():
+    """The benchmark's `overlapped_launches` arm (even launches on one stream, odd ones on a second, each with its own
+    scratch buffer) computes what the single-stream step computes, bit for bit, eagerly and from a captured graph."""
+    dev = torch.device("cuda", 0)
+    lset = bench.LinearSet("llama2-7b", dev, layers=4, seed=3)
+    run = bench.SetRunner(lset, bench.HEADLINE_GROUPS)
+    main, side = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    with torch.cuda.stream(main):
+        run.step()
+        torch.cuda.synchronize()
+        want = lset.y_all.clone()
+        lset.y_all.zero_()
+        run.step_two_streams(side)
+        torch.cuda.synchronize()
+        assert torch.equal(lset.y_all, want)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=main):
+            run.step_two_streams(side)
+        lset.y_all.zero_()
+        graph.replay()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(lset.y_all, want)
+    check_products([p for prods in run.products for p in prods])
+    assert status_clean()
