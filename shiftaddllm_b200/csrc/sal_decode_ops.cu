@@ -540,35 +540,43 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
     } else {
         const int half = hd >> 1;
         const float *cs = ra.cos_t + (size_t)pos * half, *sn = ra.sin_t + (size_t)pos * half;
-        for (int i = tid; i < G * half; i += blockDim.x) {
-            const int g = i >> (hd_shift - 1), j = i & (half - 1);
-            const size_t at = ((size_t)kvh * G + g) * hd + j;
-            const float a = rope_in<ROPE>(q, at), b = rope_in<ROPE>(q, at + half);
-            // rounded to fp16 as a separate rotary kernel would have stored it
-            qf[g * hd + j] = __half2float(__float2half_rn(a * cs[j] - b * sn[j])) * scale;
-            qf[g * hd + half + j] = __half2float(__float2half_rn(b * cs[j] + a * sn[j])) * scale;
-        }
-        if (pos_ok && t_begin <= (int)pos && (int)pos < t_begin + n) {   // this CTA's slice ends with the new token
-            __half *krow = k_cache + ((size_t)pos * kv_heads + kvh) * hd, *vrow = v_cache + ((size_t)pos * kv_heads + kvh) * hd;
-            // STAGE_V: the row also goes straight to its place among the staged rows
-            __half *ksrow = reinterpret_cast<__half *>(ks) + (size_t)(n - 1) * hd, *vsrow = reinterpret_cast<__half *>(vs) + (size_t)(n - 1) * hd;
-            for (int j = tid; j < half; j += blockDim.x) {
+        // One pass over all work items — the G query rotations, and in the CTA whose slice ends with the new token also
+        // the key rotation and the value copy — so that the loads of q, k_new and v_new are in flight together instead
+        // of one dependent round trip after the other.
+        const bool owner = pos_ok && has_newest;
+        const int nq = G * half, nk = owner ? half : 0, nv = owner ? hd : 0;
+        __half *krow = k_cache + ((size_t)pos * kv_heads + kvh) * hd, *vrow = v_cache + ((size_t)pos * kv_heads + kvh) * hd;
+        // STAGE_V: the new row also goes straight to its place among the staged rows
+        __half *ksrow = reinterpret_cast<__half *>(ks) + (size_t)(n > 0 ? n - 1 : 0) * hd;
+        __half *vsrow = reinterpret_cast<__half *>(vs) + (size_t)(n > 0 ? n - 1 : 0) * hd;
+        for (int i = tid; i < nq + nk + nv; i += blockDim.x) {
+            if (i < nq) {
+                const int g = i >> (hd_shift - 1), j = i & (half - 1);
+                const size_t at = ((size_t)kvh * G + g) * hd + j;
+                const float a = rope_in<ROPE>(q, at), b = rope_in<ROPE>(q, at + half);
+                // rounded to fp16 as a separate rotary kernel would have stored it
+                qf[g * hd + j] = __half2float(__float2half_rn(a * cs[j] - b * sn[j])) * scale;
+                qf[g * hd + half + j] = __half2float(__float2half_rn(b * cs[j] + a * sn[j])) * scale;
+            } else if (i < nq + nk) {
+                const int j = i - nq;
                 const size_t at = (size_t)kvh * hd + j;
                 const float a = rope_in<ROPE>(ra.k_new, at), b = rope_in<ROPE>(ra.k_new, at + half);
                 const __half r0 = __float2half_rn(a * cs[j] - b * sn[j]), r1 = __float2half_rn(b * cs[j] + a * sn[j]);
                 krow[j] = r0;
                 krow[half + j] = r1;
                 if (STAGE_V) ksrow[j] = r0, ksrow[half + j] = r1;
-            }
-            if (ROPE == 2) __syncthreads();   // (CTA-uniform branch) the key is fully read before it is cleared
-            for (int j = tid; j < hd; j += blockDim.x) {
+            } else {
+                const int j = i - nq - nk;
                 const __half vn = __float2half_rn(rope_in<ROPE>(ra.v_new, (size_t)kvh * hd + j));
                 vrow[j] = vn;
                 if (STAGE_V) vsrow[j] = vn;
-                if (ROPE == 2) {
-                    reinterpret_cast<acc_t *>(ra.k_new)[(size_t)kvh * hd + j] = 0;
-                    reinterpret_cast<acc_t *>(ra.v_new)[(size_t)kvh * hd + j] = 0;
-                }
+            }
+        }
+        if (ROPE == 2 && owner) {   // consumed: cleared for the next token (CTA-uniform branch; all reads above are done)
+            __syncthreads();
+            for (int j = tid; j < hd; j += blockDim.x) {
+                reinterpret_cast<acc_t *>(ra.k_new)[(size_t)kvh * hd + j] = 0;
+                reinterpret_cast<acc_t *>(ra.v_new)[(size_t)kvh * hd + j] = 0;
             }
         }
     }
