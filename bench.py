@@ -21,6 +21,8 @@ inside the timed region.  `verify` = what the timed launches computed, compared 
 region with a plain fp32 torch dequantise-and-matmul on sampled output columns.  Further legs
 (each a sub-record of the same line; `--legs` selects):
   overlapped_launches  the headline launches issued alternately on two streams (informational)
+  cta_timeline   (not in the default set; needs the measurement build of the library) per-CTA cycle counters of
+               the headline launch: dependency wait, main loop, table builds, waiting for ring data
   small_batch  the same 7B shapes with per-layer bit widths drawn from {2,3,4} (p = 0.3/0.5/0.2)
                at M in {1,4,8,16,64}: the small-batch variant of the kernel
   block_int8   the 7B shapes in the layout of the published "Lat." checkpoints (one int8 power-of-two
@@ -571,6 +573,10 @@ def run_ours(args, rank, world, device):
                                                                    for p in prods], device), 6)
         out["overlapped_launches"] = rec
 
+    # ---- per-CTA cycle counters of the headline launches (measurement build of the library only)
+    if "cta_timeline" in legs and world == 1:
+        out["cta_timeline"] = cta_timeline_record(lib, replay, device, clk.summary().get("sm_mhz") or 1965)
+
     # ---- the same step in the order a decoder's data dependencies force
     dep = None
     if "dependency_ordered" in legs:
@@ -726,6 +732,37 @@ def config5_record(args, timer, rank, world, device, peer_factory):
     torch.cuda.empty_cache()
     if "decode" in args.legs:
         rec["decoder"] = sharded_decoder_record(args, rank, world, device)
+    return rec
+
+
+def cta_timeline_record(lib, replay, device, sm_mhz):
+    """Where the thread blocks of the headline launch spend their time: the cycle counters a library built with
+    -DSAL_MEASURE keeps per CTA (SAL_LUTGEMM_LIBRARY=.../libsal_lutgemm_measure.so), read after one more replay."""
+    import numpy as np
+
+    if not hasattr(lib, "sal_debug_read"):
+        return {"unavailable": "the loaded library is not a measurement build (python -m shiftaddllm_b200.build --measure, "
+                               "then SAL_LUTGEMM_LIBRARY=shiftaddllm_b200/libsal_lutgemm_measure.so)"}
+    replay()
+    torch.cuda.synchronize(device)
+    buf = np.zeros(1024 * 8, dtype=np.uint64)
+    if lib.sal_debug_read(buf.ctypes.data, buf.nbytes) != 0:
+        return {"unavailable": "sal_debug_read failed"}
+    d = buf.reshape(512, 2, 8)[:, 0, :].astype(np.float64)       # consumer warp 0 of every CTA of the last launch
+    d = d[d[:, 4] > 0]
+    us = lambda col: d[:, col] / sm_mhz
+    rec = {"ctas": int(len(d)), "sm_mhz": sm_mhz, "units_per_cta": round(float(d[:, 4].mean()), 2),
+           "k_blocks_per_cta": round(float(d[:, 5].mean()), 2),
+           "dependency_wait_us": {"mean": round(float(us(0).mean()), 2), "first_ctas": round(float(us(0)[:16].mean()), 2),
+                                  "last_ctas": round(float(us(0)[-16:].mean()), 2)},
+           "main_loop_us": {"mean": round(float(us(3).mean()), 2), "min": round(float(us(3).min()), 2), "max": round(float(us(3).max()), 2)},
+           "of_which_table_builds_us": round(float(us(2).mean()), 2), "of_which_waiting_for_ring_data_us": round(float(us(1).mean()), 2),
+           "ctas_per_sm": round(len(d) / max(1, len(set(d[:, 6].astype(int)))), 2), "by_problem": []}
+    for p in sorted(set(d[:, 7].astype(int))):
+        m = d[:, 7].astype(int) == p
+        rec["by_problem"].append({"problem": int(p), "ctas": int(m.sum()),
+                                  "lookup_us_per_unit": round(float(((d[m, 3] - d[m, 2]) / d[m, 4]).mean() / sm_mhz), 3),
+                                  "dependency_wait_us": round(float(us(0)[m].mean()), 2)})
     return rec
 
 

@@ -277,6 +277,10 @@ int sal_plan_shift_scale(int M, int K, int N, int q, int num_groups, sal_plan_in
  * (results are then meaningless; used to time the parts); "force_per" and
  * "force_splits" override the planner's column tiles per CTA and K splits. */
 int sal_debug_set(const char *key, int value);
+/* Measurement builds only: copies the per-CTA cycle counters of the last tiled launches to `host` (at most 64 KB):
+ * 8 x uint64 per (CTA, consumer warp 0 | 7) for the first 512 CTAs — cycles at the dependency wait, cycles waiting
+ * for ring data, cycles in table builds, cycles of the main loop, units, K blocks, SM id, problem index. */
+int sal_debug_read(void *host, size_t bytes);
 #endif
 
 #ifdef __cplusplus

@@ -103,6 +103,8 @@ def load() -> ctypes.CDLL:
         if hasattr(lib, "sal_debug_set"):   # present only in measurement builds (-DSAL_MEASURE)
             lib.sal_debug_set.restype = _i
             lib.sal_debug_set.argtypes = [ctypes.c_char_p, _i]
+            lib.sal_debug_read.restype = _i
+            lib.sal_debug_read.argtypes = [_vp, _sz]
         _lib = lib
     return _lib
 

@@ -375,6 +375,17 @@ __global__ void exchange_wait_kernel(unsigned *flag, unsigned expected, int *sta
     *flag = 0u;
 }
 
+// Measurement builds keep cycle counters of the consumer warps 0 and 7 of every CTA (first 512 CTAs, row group 0):
+// [cycles at the dependency wait, cycles waiting for ring data, cycles in table builds incl. their barrier, cycles
+// of the main loop, units, K blocks, SM id, problem].  sal_debug_read copies them out.  In the product build the
+// macros vanish.
+#ifdef SAL_MEASURE
+__device__ unsigned long long g_cta_timers[1024 * 8];
+#define SAL_CYCLES() clock64()
+#else
+#define SAL_CYCLES() 0ll
+#endif
+
 // Shared-window address at which the dynamic shared memory of a kernel without static
 // shared memory starts on sm_100 (the first KB of every CTA's allocation is reserved by the
 // driver).  The ABS variant of the kernel bakes the table address into the immediate field of
@@ -721,7 +732,10 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     }
     uint32_t mbuf = 0;  // byte offset of the multiplier buffer the current tile uses (two buffers, alternating)
 
+    [[maybe_unused]] const long long t_wait0 = SAL_CYCLES();
     pdl_wait();  // activations, bias, y and the scratch buffer may be written by the previous kernel
+    [[maybe_unused]] const long long t_wait1 = SAL_CYCLES();
+    [[maybe_unused]] long long t_data = 0, t_build = 0;
 
     int st = 0;
     uint32_t phase = 0;
@@ -729,8 +743,10 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     auto process_block = [&](int kb, auto par_tag) {
         constexpr int PAR = BLK ? 0 : decltype(par_tag)::value;
         if constexpr (BLK) consumer_barrier(NCW * 32);  // one set of tables: the previous K block must be finished by all
+        [[maybe_unused]] const long long t_b0 = SAL_CYCLES();
         if (!SAL_ABLATED(P, 2)) build_block(kb, PAR, warp, std::integral_constant<int, NCW>{});
         consumer_barrier(NCW * 32);
+        t_build += SAL_CYCLES() - t_b0;
         // The activations of the next K block are asked into L1 now, so that its table build does not start with
         // a trip to L2 (no registers held meanwhile; one 16-byte line piece per lane of one warp covers the block).
         if (SWIGLU == 0 && warp == 0 && kb + 1 < kb_end && !SAL_ABLATED(P, 128)) {
@@ -774,7 +790,9 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             if constexpr (!BLK) {
 #pragma unroll
                 for (int b0 = 0; b0 < Q; b0 += PPS) {   // one ring slot: PPS planes of this unit
+                    [[maybe_unused]] const long long t_d0 = SAL_CYCLES();
                     mbar_wait(full0 + 8 * st, phase, P.status);
+                    t_data += SAL_CYCLES() - t_d0;
                     const uint32_t soff = (uint32_t)st * C::STAGE_BYTES;
                     if (!SAL_ABLATED(P, 4)) {
 #pragma unroll
@@ -928,6 +946,21 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
     }
 
     // ---------------------------------- epilogue ----------------------------------
+#ifdef SAL_MEASURE
+    if (lane == 0 && (warp == 0 || warp == NCW - 1) && blockIdx.x < 512 && blockIdx.y == 0) {
+        unsigned long long *d = g_cta_timers + (size_t)(blockIdx.x * 2 + (warp ? 1 : 0)) * 8;
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        d[0] = (unsigned long long)(t_wait1 - t_wait0);
+        d[1] = (unsigned long long)t_data;
+        d[2] = (unsigned long long)t_build;
+        d[3] = (unsigned long long)(SAL_CYCLES() - t_wait1);
+        d[4] = (unsigned long long)(u_end - u_begin);
+        d[5] = (unsigned long long)(kb_end - kb_begin);
+        d[6] = smid;
+        d[7] = (unsigned long long)pi;
+    }
+#endif
     if (ATOMIC) {
         // y is a 64-bit fixed-point accumulator: fire-and-forget integer reductions in L2, nothing to wait for, and
         // the sum does not depend on the order in which the CTAs arrive
@@ -1823,6 +1856,11 @@ int sal_workspace_status(void *workspace, void *stream) {
 }
 
 #ifdef SAL_MEASURE
+int sal_debug_read(void *host, size_t bytes) {
+    const size_t n = bytes < sizeof(g_cta_timers) ? bytes : sizeof(g_cta_timers);
+    return cuda_ok(cudaMemcpyFromSymbol(host, g_cta_timers, n)) ? SAL_OK : SAL_E_LAUNCH;
+}
+
 int sal_debug_set(const char *key, int value) {
     if (!key) return SAL_E_NULL;
     const auto eq = [&](const char *k) {
