@@ -777,12 +777,16 @@ __global__ void __launch_bounds__(ATTN_WARPS * 32) attention_split_kernel(const 
         __stcg(mine + tid * stride + hd, s_m[tid]);
         __stcg(mine + tid * stride + hd + 1, s_l[tid]);
     }
-    __threadfence();
     __syncthreads();
-    if (tid == 0) s_is_last = (atomicAdd(counters + kvh, 1u) == (unsigned)(nsplit - 1));
+    if (tid == 0) {
+        // one acquire-release add per CTA behind the barrier: the release covers the partial results the other threads
+        // stored before the barrier, the acquire those of the CTAs that arrived earlier
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(counters + kvh) : "memory");
+        s_is_last = (old == (unsigned)(nsplit - 1));
+    }
     __syncthreads();
     if (!s_is_last) return;
-    __threadfence();
     const float *all = partial + ((size_t)kvh * nsplit * G) * stride;
     // weight of every slice per query head: exp(slice max - overall max) / overall sum (empty slices: 0)
     // (one warp per query head, lane = slice: all loads of a head are in flight together)

@@ -1020,15 +1020,18 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             }
         }
     }
-    __threadfence();
+    // Arrival: ONE acquire-release add per CTA after a CTA barrier.  The release is cumulative over the barrier (the
+    // partial sums stored by the other threads happen before it), the acquire makes the partial sums of the CTAs that
+    // arrived earlier visible to this CTA's threads behind the second barrier.  (A __threadfence() in each of the 256
+    // threads on either side, as an earlier version had, made every thread wait for its own stores to settle.)
     consumer_barrier(NCW * 32);
     if (tid == 0) {
-        const unsigned old = atomicAdd(counter, 1u);
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
         s_last = (old == (unsigned)(S - 1));
     }
     consumer_barrier(NCW * 32);
     if (s_last) {
-        __threadfence();
         // The last CTA of a column range to arrive sums the partials of all K splits in
         // ascending split order (fixed, hence deterministic).  Up to 4 column tiles x 16 splits
         // = 64 independent L2 loads are in flight per thread, so the whole reduction costs one
@@ -1227,13 +1230,15 @@ __global__ void __launch_bounds__(128) lutgemv_generic_kernel(const GenericParam
     __shared__ int s_last;
     float *prow = p.partials + ((size_t)m * p.ksplit) * p.N;
     if (n < p.N) __stcg(prow + (size_t)split * p.N + n, acc);
-    __threadfence();
     __syncthreads();
     unsigned *counter = p.counters + (size_t)m * gridDim.x + blockIdx.x;
-    if (tid == 0) s_last = (atomicAdd(counter, 1u) == (unsigned)(p.ksplit - 1));
+    if (tid == 0) {   // one acquire-release add per CTA behind the barrier (see the tiled kernel)
+        unsigned old;
+        asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], 1;" : "=r"(old) : "l"(counter) : "memory");
+        s_last = (old == (unsigned)(p.ksplit - 1));
+    }
     __syncthreads();
     if (s_last) {
-        __threadfence();
         if (n < p.N) {
             float v = 0.f;
             for (int s0 = 0; s0 < p.ksplit; s0 += 8) {
