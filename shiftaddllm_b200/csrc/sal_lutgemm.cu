@@ -802,15 +802,23 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                             for (int r = 0; r < ROWS; ++r)
 #pragma unroll
                                 for (int p = 0; p < PPS; ++p) part[r][p] = part2[r][p] = 0.f;
+                            // all weight words of this half are requested before the first lookup
+                            uint32_t wv[4][PPS];
 #pragma unroll
                             for (int j = 0; j < 4; ++j) {
                                 const uint32_t wr = wrow[hp][j] + soff;
 #pragma unroll
                                 for (int p = 0; p < PPS; ++p) {
-                                    uint32_t w;
-                                    if (p == 0) w = lds_u32_imm<0>(wr);
-                                    else if (p == 1) w = lds_u32_imm<1 * BOX_COLS * 4>(wr);
-                                    else w = lds_u32_imm<2 * BOX_COLS * 4>(wr);
+                                    if (p == 0) wv[j][p] = lds_u32_imm<0>(wr);
+                                    else if (p == 1) wv[j][p] = lds_u32_imm<1 * BOX_COLS * 4>(wr);
+                                    else wv[j][p] = lds_u32_imm<2 * BOX_COLS * 4>(wr);
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+#pragma unroll
+                                for (int p = 0; p < PPS; ++p) {
+                                    const uint32_t w = wv[j][p];
                                     uint32_t e[4];
 #pragma unroll
                                     for (int t = 0; t < 4; ++t) {
