@@ -755,8 +755,7 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
             if (ROWS == 2) asm volatile("prefetch.global.L1 [%0];" ::"l"(xrow1 + (size_t)(kb + 1) * KB_FEATS + 8 * lane));
         }
         // Rolled on purpose: the body is ~100 lookups long and exists once per table half;
-        // unrolling it over the column tiles overflows the instruction cache.  acc[] is then
-        // indexed dynamically and lives in (L1-resident) local memory: two accesses per tile.
+        // unrolling it over the column tiles overflows the instruction cache.
         const int s_lo = kb == kb_begin ? t_first : 0, s_hi = kb == kb_last ? t_last + 1 : nsub;
 #pragma unroll 1
         for (int sub = s_lo; sub < s_hi; ++sub) {
@@ -943,8 +942,18 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
                 st = st_b;
                 phase = ph_b;
             }
+            if constexpr (ROWS == 1) {
+                // the tile's accumulator is picked with predicated adds, so that acc[] has static indices and stays in
+                // registers (8 of them)
 #pragma unroll
-            for (int r = 0; r < ROWS; ++r) acc[r][SAL_ABLATED(P, 32) ? 0 : sub] += a_sub[r];   // (timing only: no dynamic index)
+                for (int i = 0; i < MAX_SUB; ++i)
+                    if (i == sub) acc[0][i] += a_sub[0];
+            } else {
+                // two rows: 16 accumulators would not fit next to the rest; acc[] is indexed dynamically and lives in
+                // (L1-resident) local memory, two accesses per tile and row
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) acc[r][sub] += a_sub[r];
+            }
             if constexpr (BLK) mbuf ^= (uint32_t)(Q * 16 * LUT_ROW_BYTES);
         }
     };
