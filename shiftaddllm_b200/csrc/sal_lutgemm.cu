@@ -182,6 +182,13 @@ constexpr float SAL_FIXED_INV = 2.3283064365386963e-10f; // 2**-32
 __device__ __forceinline__ unsigned long long to_fixed(float v) { return (unsigned long long)__float2ll_rn(v * SAL_FIXED_ONE); }
 __device__ __forceinline__ float from_fixed(long long v) { return __ll2float_rn(v) * SAL_FIXED_INV; }
 
+// Read-once data (alpha): not kept in L1, so that it does not push out the few lines that are reused (the prefetched
+// activations of the next K block, the accumulators of the two-row kernel).
+__device__ __forceinline__ __half ldg_stream_f16(const __half *p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return __ushort_as_half(v);
+}
 __device__ __forceinline__ float lds_f32(uint32_t addr) {
     float v;
     asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
@@ -625,8 +632,8 @@ __global__ void __launch_bounds__(TileCfg<Q, NCW>::THREADS, (NCW <= 8 ? 2 : 1))
         const size_t off1 = off0 + (two_groups ? (size_t)Q * (size_t)N : 0);
 #pragma unroll
         for (int b = 0; b < Q; ++b) {
-            dst[0][b] = __ldg(p0 + off0 + (size_t)b * N);
-            dst[1][b] = __ldg(p0 + off1 + (size_t)b * N);
+            dst[0][b] = ldg_stream_f16(p0 + off0 + (size_t)b * N);
+            dst[1][b] = ldg_stream_f16(p0 + off1 + (size_t)b * N);
         }
     };
     __half a_next[2][Q];
