@@ -149,3 +149,22 @@ def test_synth_is_seeded_and_matches_recipe():
     assert not torch.equal(a.bWeight, c.bWeight)
     bits = synth.mixed_bits(224)
     assert set(bits) <= {2, 3, 4} and bits == synth.mixed_bits(224)
+
+
+def test_clock_sampler_summary_uses_the_timed_window():
+    """bench.ClockSampler: samples inside the marked window are the ones reported; with none inside, all samples
+    since the sampler started are used and the record says so; no samples at all gives an empty record."""
+    import bench
+
+    s = bench.ClockSampler(0)
+    s.source = "test"
+    s.rows = [(1.0, 1200, 1965, []), (2.0, 1965, 1965, ["sw_power_cap"]), (2.5, 1950, 1965, []), (4.0, 900, 1965, ["hw_slowdown"])]
+    s.t0, s.t1 = 1.5, 3.0
+    rec = s.summary()
+    assert rec["window"] == "timed steps" and rec["samples"] == 2 and rec["sm_mhz"] in (1950, 1957, 1965)
+    assert rec["reasons"] == ["sw_power_cap"] and rec["sm_max_mhz"] == 1965
+    s.t0, s.t1 = 10.0, 11.0
+    rec = s.summary()
+    assert rec["window"] == "warm-up and timed steps" and rec["samples"] == 4 and "hw_slowdown" in rec["reasons"]
+    empty = bench.ClockSampler(0).summary()
+    assert empty["samples"] == 0 and empty["sm_mhz"] is None
