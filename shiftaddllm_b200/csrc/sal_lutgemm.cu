@@ -1333,9 +1333,13 @@ struct Plan {
 // of n units touches about n / w + 1 blocks once it no longer starts on a block boundary); the split-K tail
 // grows with the number of partial sums.  Calibrated on sweeps over the launch shapes of a LLaMA-2-7B block.
 double g_cost_tb = 0.25, g_cost_r0 = 0.5, g_cost_r1 = 0.05, g_cost_rw = 0.025;  // model constants (sal_debug_set can override)
+// The launch being planned adds into accumulators (SAL_OUT_FIXED_ATOMIC): no last CTA that sums splits x tiles partial
+// sums, and a cheaper share per split (measured on a decoder's chain of launches: 8 % over the constants above).
+thread_local bool g_plan_accumulating = false;
+constexpr double COST_R1_ACCUMULATING = 0.02;
 double cta_cost(double n, int w, int c) {
     double cost = n + g_cost_tb * (n / w + (c > 1 ? 1.0 : 0.0));
-    if (c > 1) cost += g_cost_r0 + g_cost_r1 * c + g_cost_rw * c * w;
+    if (c > 1) cost += g_cost_r0 + (g_plan_accumulating ? COST_R1_ACCUMULATING * c : g_cost_r1 * c + g_cost_rw * c * w);
     return cost;
 }
 
@@ -1399,11 +1403,12 @@ struct PlanCacheEntry {
 PlanCacheEntry g_plan_cache[256];
 std::mutex g_plan_mutex;
 
-void plan_group(const sal_problem *problems, int count, int slots, bool allow_split, int cw, Plan *plans) {
+void plan_group(const sal_problem *problems, int count, int slots, bool allow_split, int cw, Plan *plans, bool accumulating) {
+    g_plan_accumulating = accumulating;
     // the plan depends on the shapes only: remember it (planning costs a few hundred microseconds)
     unsigned long long key = 1469598103934665603ull;
     const auto mix = [&](long long v) { key = (key ^ (unsigned long long)v) * 1099511628211ull; };
-    mix(count), mix(slots), mix(allow_split), mix(cw), mix(g_force_per), mix(g_force_splits);
+    mix(count), mix(slots), mix(allow_split), mix(cw), mix(g_force_per), mix(g_force_splits), mix(accumulating);
     for (int i = 0; i < count; ++i) mix(problems[i].K), mix(problems[i].N);
     PlanCacheEntry &slot = g_plan_cache[key & 255];
     {
@@ -1691,7 +1696,7 @@ int build_tiled_group(const sal_problem *problems, int count, unsigned flags, bo
     int slots = (int)(sms * (pct / 100.0) / L.row_groups);   // row groups share the SMs
     if (slots < 4 * count) slots = 4 * count;
     Plan plans[SAL_MAX_GROUP];
-    plan_group(problems, count, slots, allow_split || L.atomic_out, cw, plans);
+    plan_group(problems, count, slots, allow_split || L.atomic_out, cw, plans, L.atomic_out);
     int cta = 0;
     int counter_off = 0;
     size_t n_off = 0;
