@@ -1336,10 +1336,10 @@ double g_cost_tb = 0.25, g_cost_r0 = 0.5, g_cost_r1 = 0.05, g_cost_rw = 0.025;  
 // The launch being planned adds into accumulators (SAL_OUT_FIXED_ATOMIC): no last CTA that sums splits x tiles partial
 // sums, and a cheaper share per split (measured on a decoder's chain of launches: 8 % over the constants above).
 thread_local bool g_plan_accumulating = false;
-constexpr double COST_R1_ACCUMULATING = 0.02;
+double g_cost_r1_acc = 0.02;   // (sal_debug_set "cost_r1_acc")
 double cta_cost(double n, int w, int c) {
     double cost = n + g_cost_tb * (n / w + (c > 1 ? 1.0 : 0.0));
-    if (c > 1) cost += g_cost_r0 + (g_plan_accumulating ? COST_R1_ACCUMULATING * c : g_cost_r1 * c + g_cost_rw * c * w);
+    if (c > 1) cost += g_cost_r0 + (g_plan_accumulating ? g_cost_r1_acc * c : g_cost_r1 * c + g_cost_rw * c * w);
     return cost;
 }
 
@@ -1913,6 +1913,7 @@ int sal_debug_set(const char *key, int value) {
     else if (eq("cost_r0")) g_cost_r0 = value / 1000.0;
     else if (eq("cost_r1")) g_cost_r1 = value / 1000.0;
     else if (eq("cost_rw")) g_cost_rw = value / 1000.0;
+    else if (eq("cost_r1_acc")) g_cost_r1_acc = value / 1000.0;
     else return SAL_E_UNSUPPORTED;
     {
         std::lock_guard<std::mutex> lock(g_plan_mutex);   // remembered plans were made under the old settings
