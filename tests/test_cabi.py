@@ -91,3 +91,32 @@ def test_no_cpu_fallback(lib):
     rc = lib.sal_lutgemv_shift_scale(p, p, None, p, p, 1, 256, 64, 3, 2, 0, None, 0, None)
     assert rc == _lib.SAL_E_DEVICE
     assert lib.sal_device_ok() == _lib.SAL_E_DEVICE
+
+
+def test_planner_invariants_over_many_shapes(lib):
+    """The work split of the tiled kernel, queried without a GPU for a grid of shapes: every CTA gets at least one unit
+    (splits never exceed the units of a range), the K splits stay within the scratch layout, the ring has a slot per
+    plane group, and the CTA's shared memory lets two CTAs share an SM."""
+    info = _lib.SalPlanInfo()
+    seen_tiled = 0
+    for k in (256, 512, 768, 1024, 4096, 5120, 8192, 11008, 14336, 28672):
+        for n in (8, 256, 264, 768, 1000, 4096, 11008, 32000):
+            for q in (1, 2, 3, 4):
+                for m in (1, 2, 7, 16, 64):
+                    if k % 128:
+                        continue
+                    rc = lib.sal_plan_shift_scale(m, k, n, q, k // 128, ctypes.byref(info))
+                    assert rc == 0, (m, k, n, q, rc)
+                    if not info.tiled:
+                        assert info.ctas >= 1
+                        continue
+                    seen_tiled += 1
+                    tiles = (n + 255) // 256
+                    assert 1 <= info.ranges <= tiles
+                    assert 1 <= info.splits <= 64
+                    units_per_range = -(-tiles // info.ranges) * (k // 256)      # upper bound for the widest range
+                    assert info.splits <= units_per_range
+                    assert info.ctas >= info.ranges
+                    assert info.stages >= (2 if q == 4 else 1)
+                    assert info.smem_bytes <= 115712
+    assert seen_tiled > 500
